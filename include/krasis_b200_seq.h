@@ -71,6 +71,14 @@ KB2SEQ_API int kb2_seq_latent_window_attn(const float* q_abs, const float* proj,
 KB2SEQ_API int kb2_seq_conv_silu(const float* proj, long long ldp, int T, int S, int C, int K, const float* taps, float* tail,
                                  const int* seq_of, const int* cu, const int* slots, float* out, void* stream);
 
+/* The same with a bias added to proj before the convolution (null: none; the carried tail holds biased inputs) and act 1: silu, 0: none */
+KB2SEQ_API int kb2_seq_conv(const float* proj, long long ldp, int T, int S, int C, int K, const float* taps, const float* bias, int act,
+                            float* tail, const int* seq_of, const int* cu, const int* slots, float* out, void* stream);
+
+/* x += y_mult * y (y may be null); h = x / sqrt(mean(x^2) + eps) * (w_shift + w) (h may be null; h == x with y null: in place, fp32) */
+KB2SEQ_API int kb2_seq_residual_scale_rms(float* x, const float* y, float y_mult, const float* w, float w_shift, void* h, int dt_h, int T,
+                                          int W, float eps, void* stream);
+
 /* gated delta rule over each sequence's portion; state [slots][H][dk][dv] fp32 is read and written back.
  * scratch (fp32, 2 T Hk dk + 2 T H + T H dv + 4 elements, 16-byte aligned) selects the register-state kernels when dk is 32, 64 or
  * 128 and dv a multiple of 32; with scratch == NULL, or other sizes, one block per (sequence, head) keeps the state in shared memory. */
@@ -78,6 +86,15 @@ KB2SEQ_API int kb2_seq_delta_rule(const float* conv, int C, const float* proj, l
                                   int S, int H, int Hk, int dk, int dv, const float* A_log, const float* dt_bias, const float* norm_w,
                                   float eps, float* state, const int* cu, const int* slots, float* scratch, void* out, int dt_out,
                                   void* stream);
+
+/* The delta rule with one decay per (token, head, key channel): S <- diag(g) S with g = exp(-exp(A_log[h]) softplus(decay_in[t, h dk + i]
+ * + dt_bias[h dk + i])), then u = beta (v - S^T k), S <- S + k u^T, o = S^T q.  beta_in [T, ldb] holds H write-strength logits per row,
+ * decay_in [T, lda] H dk decay inputs, gate_in [T, ldg] H dv output-gate inputs (gate_act 0: silu, 1: sigmoid).  scratch as above with
+ * T H dk more elements. */
+KB2SEQ_API int kb2_seq_delta_rule_ch(const float* conv, int C, const float* beta_in, long long ldb, const float* decay_in, long long lda,
+                                     const float* gate_in, long long ldg, int gate_act, int T, int S, int H, int Hk, int dk, int dv,
+                                     const float* A_log, const float* dt_bias, const float* norm_w, float eps, float* state, const int* cu,
+                                     const int* slots, float* scratch, void* out, int dt_out, void* stream);
 
 /* ---- second part (csrc/seq_mix.cu): per-head key/value caches, multi-map attention, gated linear units, routed experts ---- */
 
@@ -88,20 +105,22 @@ KB2SEQ_API int kb2_seq_residual_add_norm(float* x, const float* y, const float* 
 /* proj [T, ldp] fp32 = [q: H x M x d | k: G x M x d | v: G x dv | ...]: H query heads with M maps each, G key/value heads (0: the layer
  * reads another layer's cache).  bias (same column order, may be null) is added; every q / k vector of d is RMS-normed with the weight
  * qw / kw [d] (null: no norm) and its first rot_dims dimensions are rotated as interleaved pairs by position * freq[i].  q is written
- * back in place; k [G M d] and v [G dv] go to the cache rows of the tokens' positions. */
+ * back in place; k [G M d] and v [G dv] go to the cache rows of the tokens' positions.  norm_whole 1: one root mean square over the whole
+ * of q (and of k) with weights qw [H M d] / kw [G M d].  rot_half 1: dimension i turns with i + rot_dims / 2 instead of 2i with 2i + 1. */
 KB2SEQ_API int kb2_seq_head_kv_prep(float* proj, long long ldp, int T, int H, int G, int M, int d, int dv, const float* bias,
                                     const float* qw, const float* kw, float eps, const double* freq, int rot_dims, const int* positions,
                                     const int* seq_of, const int* pages, int max_pages, int page_size, void* kc, void* vc, int dt_cache,
-                                    void* stream);
+                                    int norm_whole, int rot_half, void* stream);
 
 /* out [T, H, M, dv] fp32: softmax attention of each (head, map) query over the keys j <= pos of its sequence that lie in the same
  * chunk (chunk > 0: floor(j / chunk) == floor(pos / chunk)) and within 0 <= pos - j < window.  Head h reads key/value head h / (H / G);
  * map m reads the keys of map m; all maps read the same values.  cu / skip_from and nsplit / part_acc [T H M][nsplit][dv] /
- * part_ml [T H M][nsplit][2] as in kb2_seq_latent_window_attn, except that the pieces are merged by kb2_seq_attn_finish. */
+ * part_ml [T H M][nsplit][2] as in kb2_seq_latent_window_attn, except that the pieces are merged by kb2_seq_attn_finish.
+ * softcap > 0: a score s (after the scale) becomes softcap tanh(s / softcap). */
 KB2SEQ_API int kb2_seq_paged_attn(const float* proj, long long ldp, int T, int H, int G, int M, int d, int dv, const void* kc,
                                   const void* vc, int dt_cache, const int* positions, const int* seq_of, const int* pages, int max_pages,
                                   int page_size, float scale, int chunk, int window, float* out, int nsplit, float* part_acc,
-                                  float* part_ml, const int* cu, int skip_from, void* stream);
+                                  float* part_ml, const int* cu, int skip_from, float softcap, void* stream);
 
 /* out[t, h, :] = f * sum_m coef[m] a[t, h, m, :] (coef null: ones), f = post_scale / rms(sum) if unit_norm, times sigmoid(gate[t * ldg + h])
  * if gate is given.  nsplit > 1: a is merged from part_acc / part_ml first. */
@@ -110,15 +129,16 @@ KB2SEQ_API int kb2_seq_attn_finish(const float* a, const float* part_acc, const 
                                    void* out, int dt_out, const int* seq_of, const int* cu, int skip_from, void* stream);
 
 /* in [rows, ld_in] = [gate: F | up: F]; out [rows, F].  kind 0: gelu_tanh(g) u, 1: silu(g) u, 2: g' sigmoid(alpha g') (u' + 1) with
- * g' = min(g, limit), u' = clamp(u, -limit, limit).  n_tiles (device, may be null): only n_tiles[0] * tile_rows rows are computed. */
+ * g' = min(g, limit), u' = clamp(u, -limit, limit), 3: relu(g)^2 of in [rows, ld_in >= F] (no up half).  n_tiles (device, may be null): only n_tiles[0] * tile_rows rows are computed. */
 KB2SEQ_API int kb2_seq_glu(const void* in, int dt_in, long long ld_in, void* out, int dt_out, long long rows, int F, int kind, float limit,
                            float alpha, const int* n_tiles, int tile_rows, void* stream);
 
 /* Router: z [T, ldz] fp32 logits of E outputs -> ids [T, top], weights [T, top].  score_kind 0 softmax, 1 sigmoid; choice = score +
- * correction (may be null); groups > 1: E / groups neighbours form a group, only the `keep` groups with the largest maximal choice can
- * be chosen; weights are the chosen scores (without correction), divided by their sum if renorm, times out_scale. */
+ * correction (may be null); groups > 1: E / groups neighbours form a group, only the `keep` groups with the largest group score
+ * (group_kind 0: the group's largest choice, 1: the sum of its two largest) can be chosen; weights are the chosen scores (without
+ * correction), divided by their sum (+ 1e-20) if renorm, times out_scale. */
 KB2SEQ_API int kb2_seq_route(const float* z, long long ldz, int T, int E, const float* correction, int score_kind, int groups, int keep,
-                             int top, int renorm, float out_scale, int* ids, float* weights, void* stream);
+                             int top, int renorm, float out_scale, int* ids, float* weights, int group_kind, void* stream);
 
 /* Routed experts.  moe_bin: slots = T * top entries of ids; ids outside [0, E) are left out (identity experts).  Each expert's slots
  * form a run of rows padded to whole tiles of tile_rows (a multiple of kb2_seq_moe_tile_rows()): offs [E + 1], tile_expert [max_rows / tile], n_tiles [1],
@@ -135,10 +155,11 @@ KB2SEQ_API int kb2_seq_moe_gemm(const void* A, int dtA, long long lda, const int
 /* Few slots, no binning: C[slot, :] = A[slot / div, :] * B[ids[slot]]^T; slots with ids outside [0, E) are skipped. */
 KB2SEQ_API int kb2_seq_moe_gemv(const void* A, int dtA, long long lda, int div, const int* ids, int E, const void* B, int dtB, long long ldb,
                                 long long sB, void* C, int dtC, long long ldc, int slots, int N, int K, void* stream);
-/* out[t, :] = sum_k weights[t, k] * (y[row of slot (t, k)] | h[t] if E <= ids < E + ident) + shared[t] (may be null); pos_of_slot null:
- * the row of a slot is the slot itself. */
+/* out[t, :] = sum_k weights[t, k] * (y[row of slot (t, k)] | h[t] if E <= ids < E + ident) + f shared[t] (may be null); pos_of_slot null:
+ * the row of a slot is the slot itself.  f = sigmoid(shared_gate[t * ldsg]), or 1 when shared_gate is null. */
 KB2SEQ_API int kb2_seq_moe_combine(const float* y, const int* pos_of_slot, const int* ids, const float* weights, int T, int top, int E,
-                                   int ident, const void* h, int dt_h, const float* shared, float* out, int W, void* stream);
+                                   int ident, const void* h, int dt_h, const float* shared, float* out, int W, const float* shared_gate,
+                                   long long ldsg, void* stream);
 
 #ifdef __cplusplus
 }

@@ -21,14 +21,18 @@ namespace kb2seq {
 
 // ------------------------------------------------------------------------------------------------ query / key / value preparation
 // proj [T, ldp] fp32 = [q: H x M x d | k: G x M x d | v: G x dv | ...] (G == 0: the layer reads another layer's cache and has no k, v).
-// A warp per vector of d.
+// A warp per vector of d.  norm_whole 0: every vector is normed by itself with the weight qw / kw [d]; 1: one root mean square over all
+// of q (and one over all of k) with weights of the projection's size.  rot_half 0: dimension 2j turns with 2j + 1; 1: j with
+// j + rot_dims / 2.
 __global__ void __launch_bounds__(256) head_kv_prep_kernel(float* __restrict__ proj, long long ldp, int H, int G, int M, int d, int dv,
                                                            const float* __restrict__ bias, const float* __restrict__ qw,
                                                            const float* __restrict__ kw, float eps, const double* __restrict__ freq,
                                                            int rot_dims, const int* __restrict__ positions,
                                                            const int* __restrict__ seq_of, const int* __restrict__ pages, int max_pages,
-                                                           int page_size, void* __restrict__ kc, void* __restrict__ vc, int dt_cache) {
+                                                           int page_size, void* __restrict__ kc, void* __restrict__ vc, int dt_cache,
+                                                           int norm_whole, int rot_half) {
   extern __shared__ float rot_tab[];          // [rot_dims / 2][2]: cos, sin of the token's position, shared by all its vectors
+  __shared__ float red[32];
   const long long t = blockIdx.x;
   const int pos = positions[t];
   float* p = proj + t * ldp;
@@ -36,14 +40,30 @@ __global__ void __launch_bounds__(256) head_kv_prep_kernel(float* __restrict__ p
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int nq = H * M, nvec = (H + G) * M, half = rot_dims >> 1;
   for (int j = threadIdx.x; j < half; j += blockDim.x) rot_cs(pos, freq[j], 1.f, &rot_tab[2 * j], &rot_tab[2 * j + 1]);
+  float rstd_q = 1.f, rstd_k = 1.f;
+  if (norm_whole) {
+    const int nqe = nq * d, nke = (nvec - nq) * d;
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < nqe + nke; i += blockDim.x) {
+      const float v = p[i] + (bias ? bias[i] : 0.f);
+      if (i < nqe) sq = fmaf(v, v, sq); else sk = fmaf(v, v, sk);
+    }
+    sq = block_sum(sq, red);
+    sk = block_sum(sk, red);
+    if (qw != nullptr) rstd_q = 1.f / sqrtf(sq / (float)nqe + eps);
+    if (kw != nullptr && nke > 0) rstd_k = 1.f / sqrtf(sk / (float)nke + eps);
+  }
   __syncthreads();
   for (int vi = warp; vi < nvec; vi += nw) {
     const bool is_q = vi < nq;
     float* x = p + (long long)vi * d;
     const float* b = bias ? bias + (long long)vi * d : nullptr;
     const float* w = is_q ? qw : kw;
+    if (norm_whole && w != nullptr) w += (long long)(is_q ? vi : vi - nq) * d;
     float rstd = 1.f;
-    if (w != nullptr) {
+    if (norm_whole) {
+      rstd = is_q ? rstd_q : rstd_k;
+    } else if (w != nullptr) {
       float ss = 0.f;
       for (int i = lane; i < d; i += 32) {
         const float v = x[i] + (b ? b[i] : 0.f);
@@ -54,21 +74,22 @@ __global__ void __launch_bounds__(256) head_kv_prep_kernel(float* __restrict__ p
     }
     const long long krow = (slot * G * M + (vi - nq)) * d;      // used for keys only
     for (int j = lane; j < half; j += 32) {
-      float u = x[2 * j] + (b ? b[2 * j] : 0.f), v = x[2 * j + 1] + (b ? b[2 * j + 1] : 0.f);
+      const int iu = rot_half ? j : 2 * j, iv = rot_half ? j + half : 2 * j + 1;
+      float u = x[iu] + (b ? b[iu] : 0.f), v = x[iv] + (b ? b[iv] : 0.f);
       u *= rstd;
       v *= rstd;
       if (w != nullptr) {
-        u *= w[2 * j];
-        v *= w[2 * j + 1];
+        u *= w[iu];
+        v *= w[iv];
       }
       const float c = rot_tab[2 * j], s = rot_tab[2 * j + 1];
       const float ru = u * c - v * s, rv = v * c + u * s;
       if (is_q) {
-        x[2 * j] = ru;
-        x[2 * j + 1] = rv;
+        x[iu] = ru;
+        x[iv] = rv;
       } else {
-        st_dt(kc, dt_cache, krow + 2 * j, ru);
-        st_dt(kc, dt_cache, krow + 2 * j + 1, rv);
+        st_dt(kc, dt_cache, krow + iu, ru);
+        st_dt(kc, dt_cache, krow + iv, rv);
       }
     }
     for (int i = rot_dims + lane; i < d; i += 32) {
@@ -90,7 +111,7 @@ __global__ void __launch_bounds__(kPAThreads) paged_attn_kernel(
     const float* __restrict__ proj, long long ldp, int H, int G, int M, int d, int dv, int RB, const void* __restrict__ kc,
     const void* __restrict__ vc, int dt_cache, const int* __restrict__ positions, const int* __restrict__ seq_of,
     const int* __restrict__ pages, int max_pages, int page_size, float scale, int chunk, int window, float* __restrict__ out, int nsplit,
-    float* __restrict__ part_acc, float* __restrict__ part_ml, const int* __restrict__ cu, int skip_from) {
+    float* __restrict__ part_acc, float* __restrict__ part_ml, const int* __restrict__ cu, int skip_from, float softcap) {
   extern __shared__ __align__(16) float sm[];
   constexpr int KT = kPAKT;
   const long long t = blockIdx.x;
@@ -172,6 +193,7 @@ __global__ void __launch_bounds__(kPAThreads) paged_attn_kernel(
         float dot = 0.f;
         for (int dd = 0; dd < d; ++dd) dot = fmaf(qh[dd], kk[dd], dot);
         sc = dot * scale;
+        if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
       }
       const float m_old = m_run[r];
       const float m_new = fmaxf(m_old, warp_max(sc));
@@ -283,8 +305,10 @@ __global__ void __launch_bounds__(256) attn_finish_kernel(const float* __restric
 
 // ------------------------------------------------------------------------------------------------ gated linear units
 // in [rows, 2 F] = [gate | up].  kind 0: gelu_tanh(g) u; 1: silu(g) u; 2: g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit),
-// u' = clamp(u, -limit, limit).  With n_tiles given only the first n_tiles[0] * tile_rows rows are computed.
+// u' = clamp(u, -limit, limit); 3: relu(g)^2 of in [rows, F] alone (no up half).  With n_tiles given only the first
+// n_tiles[0] * tile_rows rows are computed.
 __device__ __forceinline__ float glu_value(float g, float u, int kind, float limit, float alpha) {
+  if (kind == 3) return g > 0.f ? g * g : 0.f;
   if (kind == 0) return gelu_tanh(g) * u;
   if (kind == 1) return silu(g) * u;
   g = fminf(g, limit);
@@ -298,7 +322,7 @@ __global__ void glu_kernel(const void* __restrict__ in, int dt_in, long long ld_
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / F;
     const int f = (int)(i - r * F);
-    st_dt(out, dt_out, i, glu_value(ld_dt(in, dt_in, r * ld_in + f), ld_dt(in, dt_in, r * ld_in + F + f), kind, limit, alpha));
+    st_dt(out, dt_out, i, glu_value(ld_dt(in, dt_in, r * ld_in + f), kind == 3 ? 0.f : ld_dt(in, dt_in, r * ld_in + F + f), kind, limit, alpha));
   }
 }
 
@@ -313,7 +337,7 @@ __global__ void glu_bf16x8_kernel(const bf16* __restrict__ in, long long ld_in, 
     const int f = (int)(i - r * F8) << 3;
     float a[8], b[8];
     unpack8(*reinterpret_cast<const uint4*>(in + r * ld_in + f), a);
-    unpack8(*reinterpret_cast<const uint4*>(in + r * ld_in + F + f), b);
+    if (kind != 3) unpack8(*reinterpret_cast<const uint4*>(in + r * ld_in + F + f), b);
     uint4 o;
     __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
@@ -325,12 +349,13 @@ __global__ void glu_bf16x8_kernel(const bf16* __restrict__ in, long long ld_in, 
 
 // ------------------------------------------------------------------------------------------------ router
 // A warp per token.  s = softmax(z) (score_kind 0) or sigmoid(z) (1) over the E router outputs; choice c = s + correction; with
-// groups > 1 only the experts of the `keep` groups with the largest maximal choice stay in play; the `top` largest choices are taken
-// (ties: lower index); weights are the chosen s, divided by their sum if renorm, times out_scale.
+// groups > 1 only the experts of the `keep` groups with the largest group score (their largest choice, or the sum of their two largest)
+// stay in play; the `top` largest choices are taken (ties: lower index); weights are the chosen s, divided by their sum (+ 1e-20) if
+// renorm, times out_scale.
 __global__ void __launch_bounds__(128) route_topk_kernel(const float* __restrict__ z, long long ldz, int T, int E,
                                                          const float* __restrict__ correction, int score_kind, int groups, int keep,
                                                          int top, int renorm, float out_scale, int* __restrict__ ids,
-                                                         float* __restrict__ weights) {
+                                                         float* __restrict__ weights, int group_kind) {
   extern __shared__ float rsm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const long long t = (long long)blockIdx.x * nw + warp;
@@ -358,10 +383,13 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const float* __restrict
   __syncwarp();
   if (groups > 1 && keep < groups) {
     const int gs = E / groups;
-    for (int gi = lane; gi < groups; gi += 32) {
-      float mx = -INFINITY;
-      for (int e = gi * gs; e < (gi + 1) * gs; ++e) mx = fmaxf(mx, c[e]);
-      gsc[gi] = mx;
+    for (int gi = lane; gi < groups; gi += 32) {      // group_kind 0: largest choice of the group; 1: sum of its two largest
+      float mx = -INFINITY, m2 = -INFINITY;
+      for (int e = gi * gs; e < (gi + 1) * gs; ++e) {
+        const float v = c[e];
+        if (v > mx) { m2 = mx; mx = v; } else if (v > m2) m2 = v;
+      }
+      gsc[gi] = (group_kind == 1 && m2 != -INFINITY) ? mx + m2 : mx;
     }
     __syncwarp();
     // the keep best groups get +inf as a mark, one after the other
@@ -409,7 +437,7 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const float* __restrict
     __syncwarp();
   }
   if (lane == 0) {
-    const float f = (renorm ? 1.f / wsum : 1.f) * out_scale;
+    const float f = (renorm ? 1.f / (wsum + 1e-20f) : 1.f) * out_scale;
     if (f != 1.f)
       for (int it = 0; it < top; ++it) weights[t * top + it] *= f;
   }
@@ -548,11 +576,14 @@ __global__ void __launch_bounds__(256) moe_gemv_kernel(const TA* __restrict__ A,
   if (lane == 0) stf(C, (long long)slot * ldc + n, acc);
 }
 
-// out[t, :] = sum_k w[t, k] * (expert row of slot (t, k) | h[t, :] for an identity expert) + shared[t, :], k in selection order
+// out[t, :] = sum_k w[t, k] * (expert row of slot (t, k) | h[t, :] for an identity expert) + sigmoid(shared_gate[t]) shared[t, :] (gate
+// null: 1), k in selection order
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of_slot, const int* __restrict__ ids,
                                    const float* __restrict__ weights, int top, int E, int ident, const void* __restrict__ h, int dt_h,
-                                   const float* __restrict__ shared, float* __restrict__ out, int W) {
+                                   const float* __restrict__ shared, float* __restrict__ out, int W,
+                                   const float* __restrict__ shared_gate, long long ldsg) {
   const long long t = blockIdx.x;
+  const float sgate = shared_gate != nullptr ? 1.f / (1.f + expf(-shared_gate[t * ldsg])) : 1.f;   // the shared expert's weight for this token
   if ((W & 3) == 0 && dt_h == 1) {           // four columns per thread, 16-byte loads of the expert rows; same order of the sum over k
     for (int d = threadIdx.x * 4; d < W; d += blockDim.x * 4) {
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -572,7 +603,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
       }
       if (shared != nullptr) {
         const float4 r = *reinterpret_cast<const float4*>(shared + t * W + d);
-        v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+        v.x = fmaf(sgate, r.x, v.x); v.y = fmaf(sgate, r.y, v.y); v.z = fmaf(sgate, r.z, v.z); v.w = fmaf(sgate, r.w, v.w);
       }
       *reinterpret_cast<float4*>(out + t * W + d) = v;
     }
@@ -591,7 +622,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
         v = fmaf(w, ld_dt(h, dt_h, t * W + d), v);
       }
     }
-    if (shared != nullptr) v += shared[t * W + d];
+    if (shared != nullptr) v = fmaf(sgate, shared[t * W + d], v);
     out[t * W + d] = v;
   }
 }
@@ -605,13 +636,13 @@ extern "C" {
 KB2SEQ_API int kb2_seq_head_kv_prep(float* proj, long long ldp, int T, int H, int G, int M, int d, int dv, const float* bias,
                                     const float* qw, const float* kw, float eps, const double* freq, int rot_dims, const int* positions,
                                     const int* seq_of, const int* pages, int max_pages, int page_size, void* kc, void* vc, int dt_cache,
-                                    void* stream) {
+                                    int norm_whole, int rot_half, void* stream) {
   if (!proj || !positions || !seq_of || !pages || T <= 0 || H <= 0 || G < 0 || M <= 0 || d <= 0 || dv < 0 || rot_dims < 0 ||
       rot_dims > d || (rot_dims & 1) || (rot_dims && !freq) || page_size <= 0 || max_pages <= 0 || bad_dt(dt_cache) ||
       (G > 0 && (!kc || !vc)))
     return failf(KB2SEQ_ERR_VALUE, "head_kv_prep: bad argument");
   head_kv_prep_kernel<<<T, 256, (size_t)rot_dims * 4, (cudaStream_t)stream>>>(proj, ldp, H, G, M, d, dv, bias, qw, kw, eps, freq, rot_dims, positions, seq_of,
-                                                           pages, max_pages, page_size, kc, vc, dt_cache);
+                                                           pages, max_pages, page_size, kc, vc, dt_cache, norm_whole, rot_half);
   SEQ_LAUNCHED();
   return KB2SEQ_OK;
 }
@@ -619,9 +650,9 @@ KB2SEQ_API int kb2_seq_head_kv_prep(float* proj, long long ldp, int T, int H, in
 KB2SEQ_API int kb2_seq_paged_attn(const float* proj, long long ldp, int T, int H, int G, int M, int d, int dv, const void* kc,
                                   const void* vc, int dt_cache, const int* positions, const int* seq_of, const int* pages, int max_pages,
                                   int page_size, float scale, int chunk, int window, float* out, int nsplit, float* part_acc,
-                                  float* part_ml, const int* cu, int skip_from, void* stream) {
+                                  float* part_ml, const int* cu, int skip_from, float softcap, void* stream) {
   if (!proj || !kc || !vc || !positions || !seq_of || !pages || !out || T <= 0 || H <= 0 || G <= 0 || H % G || M <= 0 || d <= 0 ||
-      dv <= 0 || window <= 0 || chunk < 0 || page_size <= 0 || bad_dt(dt_cache))
+      dv <= 0 || window <= 0 || chunk < 0 || page_size <= 0 || bad_dt(dt_cache) || !(softcap >= 0.f))
     return failf(KB2SEQ_ERR_VALUE, "paged_attn: bad argument");
   if (nsplit < 1 || nsplit > 1024 || (nsplit > 1 && (!part_acc || !part_ml))) return failf(KB2SEQ_ERR_VALUE, "paged_attn: bad key split");
   if (dv > kPAThreads * kPAAcc) return failf(KB2SEQ_ERR_VALUE, "paged_attn: value size %d > %d", dv, kPAThreads * kPAAcc);
@@ -638,7 +669,7 @@ KB2SEQ_API int kb2_seq_paged_attn(const float* proj, long long ldp, int T, int H
   if ((long long)G * nrb > 65535) return failf(KB2SEQ_ERR_VALUE, "paged_attn: too many heads");
   paged_attn_kernel<<<dim3(T, G * nrb, nsplit), kPAThreads, smem, (cudaStream_t)stream>>>(
       proj, ldp, H, G, M, d, dv, RB, kc, vc, dt_cache, positions, seq_of, pages, max_pages, page_size, scale, chunk, window, out, nsplit,
-      part_acc, part_ml, cu, skip_from);
+      part_acc, part_ml, cu, skip_from, softcap);
   SEQ_LAUNCHED();
   return KB2SEQ_OK;
 }
@@ -660,7 +691,7 @@ KB2SEQ_API int kb2_seq_attn_finish(const float* a, const float* part_acc, const 
 
 KB2SEQ_API int kb2_seq_glu(const void* in, int dt_in, long long ld_in, void* out, int dt_out, long long rows, int F, int kind, float limit,
                            float alpha, const int* n_tiles, int tile_rows, void* stream) {
-  if (!in || !out || rows <= 0 || F <= 0 || ld_in < 2 * F || kind < 0 || kind > 2 || bad_dt(dt_in) || bad_dt(dt_out))
+  if (!in || !out || rows <= 0 || F <= 0 || ld_in < (kind == 3 ? F : 2 * F) || kind < 0 || kind > 3 || bad_dt(dt_in) || bad_dt(dt_out))
     return failf(KB2SEQ_ERR_VALUE, "glu: bad argument");
   if (dt_in == 1 && dt_out == 1 && F % 8 == 0 && ld_in % 8 == 0 && !((uintptr_t)in & 15) && !((uintptr_t)out & 15)) {
     const long long n8 = rows * (F / 8);
@@ -677,8 +708,8 @@ KB2SEQ_API int kb2_seq_glu(const void* in, int dt_in, long long ld_in, void* out
 }
 
 KB2SEQ_API int kb2_seq_route(const float* z, long long ldz, int T, int E, const float* correction, int score_kind, int groups, int keep,
-                             int top, int renorm, float out_scale, int* ids, float* weights, void* stream) {
-  if (!z || !ids || !weights || T <= 0 || E <= 0 || top <= 0 || top > E || score_kind < 0 || score_kind > 1 || groups < 1 ||
+                             int top, int renorm, float out_scale, int* ids, float* weights, int group_kind, void* stream) {
+  if (!z || !ids || !weights || T <= 0 || E <= 0 || top <= 0 || top > E || score_kind < 0 || score_kind > 1 || groups < 1 || group_kind < 0 || group_kind > 1 ||
       E % groups || keep < 1 || keep > groups)
     return failf(KB2SEQ_ERR_VALUE, "route: bad argument (E=%d top=%d groups=%d keep=%d)", E, top, groups, keep);
   if ((long long)keep * (E / groups) < top) return failf(KB2SEQ_ERR_VALUE, "route: the kept groups hold fewer than top experts");
@@ -686,7 +717,7 @@ KB2SEQ_API int kb2_seq_route(const float* z, long long ldz, int T, int E, const 
   if (smem > 200 * 1024) return failf(KB2SEQ_ERR_VALUE, "route: %d router outputs too many", E);
   if (smem > 48 * 1024) SEQ_CUDA(cudaFuncSetAttribute(route_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   route_topk_kernel<<<(T + 3) / 4, 128, smem, (cudaStream_t)stream>>>(z, ldz, T, E, correction, score_kind, groups, keep, top, renorm,
-                                                                      out_scale, ids, weights);
+                                                                      out_scale, ids, weights, group_kind);
   SEQ_LAUNCHED();
   return KB2SEQ_OK;
 }
@@ -761,10 +792,11 @@ KB2SEQ_API int kb2_seq_moe_gemv(const void* A, int dtA, long long lda, int div, 
 }
 
 KB2SEQ_API int kb2_seq_moe_combine(const float* y, const int* pos_of_slot, const int* ids, const float* weights, int T, int top, int E,
-                                   int ident, const void* h, int dt_h, const float* shared, float* out, int W, void* stream) {
+                                   int ident, const void* h, int dt_h, const float* shared, float* out, int W, const float* shared_gate,
+                                   long long ldsg, void* stream) {
   if (!ids || !weights || !out || T <= 0 || top <= 0 || E < 0 || ident < 0 || W <= 0 || (E > 0 && !y) || (ident > 0 && (!h || bad_dt(dt_h))))
     return failf(KB2SEQ_ERR_VALUE, "moe_combine: bad argument");
-  moe_combine_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(y, pos_of_slot, ids, weights, top, E, ident, h, dt_h, shared, out, W);
+  moe_combine_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(y, pos_of_slot, ids, weights, top, E, ident, h, dt_h, shared, out, W, shared_gate, ldsg);
   SEQ_LAUNCHED();
   return KB2SEQ_OK;
 }

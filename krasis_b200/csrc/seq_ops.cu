@@ -317,6 +317,31 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ 
   for (int d = threadIdx.x; d < W; d += blockDim.x) st_dt(h, dt_h, row * W + d, (rowbuf[d] - mean) * rstd * wb[d] + (bb != nullptr ? bb[d] : 0.f));
 }
 
+// One block per token row.  x (fp32) += y_mult * y (y may be null); then h = x / sqrt(mean(x^2) + eps) * (w_shift + w) if h is given
+// (w_shift 1: a weight stored around zero).  h may be x itself when y is null and dt_h is fp32 (a norm in place).
+__global__ void __launch_bounds__(256) residual_scale_rms_kernel(float* x, const float* __restrict__ y, float y_mult,
+                                                                 const float* __restrict__ w, float w_shift, void* h, int dt_h, int W,
+                                                                 float eps) {
+  extern __shared__ float rowbuf[];
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  float* xr = x + row * W;
+  float s = 0.f;
+  for (int d = threadIdx.x; d < W; d += blockDim.x) {
+    float v = xr[d];
+    if (y != nullptr) {
+      v = fmaf(y_mult, y[row * W + d], v);
+      xr[d] = v;
+    }
+    rowbuf[d] = v;
+    s = fmaf(v, v, s);
+  }
+  if (h == nullptr) return;
+  s = block_sum(s, red);
+  const float rstd = 1.f / sqrtf(s / (float)W + eps);
+  for (int d = threadIdx.x; d < W; d += blockDim.x) st_dt(h, dt_h, row * W + d, rowbuf[d] * rstd * (w_shift + w[d]));
+}
+
 // ------------------------------------------------------------------------------------------------ elementwise
 __global__ void act_mul_kernel(const void* __restrict__ in, int dt_in, void* __restrict__ out, int dt_out, long long T, int F) {
   const long long t = blockIdx.y;
@@ -571,11 +596,13 @@ __global__ void __launch_bounds__(128) latent_attn_combine_kernel(const float* _
 }
 
 // ------------------------------------------------------------------------------------------------ short convolution + delta rule
-// y[t, c] = silu(sum_j taps[c, j] * x[i - (K - 1) + j, c]) with i the token's index in its portion; inputs before the portion come
-// from the sequence's carried tail (the last K - 1 inputs of earlier portions, zeros at the start of a sequence).
+// y[t, c] = act(sum_j taps[c, j] * x[i - (K - 1) + j, c]) with i the token's index in its portion and x = proj + bias (bias may be null);
+// act 1: silu, 0: none.  Inputs before the portion come from the sequence's carried tail (the last K - 1 inputs of earlier portions,
+// bias included; zeros at the start of a sequence).
 __global__ void conv_silu_kernel(const float* __restrict__ proj, long long ldp, int C, int K, const float* __restrict__ taps,
                                  const float* __restrict__ tail, const int* __restrict__ seq_of, const int* __restrict__ cu,
-                                 const int* __restrict__ slots, long long T, float* __restrict__ out) {
+                                 const int* __restrict__ slots, long long T, float* __restrict__ out, const float* __restrict__ bias,
+                                 int act) {
   const long long t = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
@@ -583,51 +610,57 @@ __global__ void conv_silu_kernel(const float* __restrict__ proj, long long ldp, 
   const int s = seq_of[t];
   const int i = (int)(t - cu[s]);
   const float* tl = tail + ((long long)slots[s] * C + c) * (K - 1);
+  const float b = bias != nullptr ? bias[c] : 0.f;
   float acc = 0.f;
   for (int j = 0; j < K; ++j) {
     const int src = i - (K - 1) + j;
-    const float xv = src >= 0 ? proj[(t - i + src) * ldp + c] : tl[(K - 1) + src];
+    const float xv = src >= 0 ? proj[(t - i + src) * ldp + c] + b : tl[(K - 1) + src];
     acc = fmaf(taps[(long long)c * K + j], xv, acc);
   }
-  out[idx] = silu(acc);
+  out[idx] = act ? silu(acc) : acc;
 }
 
 // after the convolution: the tail becomes the last K - 1 inputs seen so far (one thread per (sequence, channel), ascending order)
 __global__ void conv_tail_kernel(const float* __restrict__ proj, long long ldp, int C, int K, float* __restrict__ tail,
-                                 const int* __restrict__ cu, const int* __restrict__ slots, int S) {
+                                 const int* __restrict__ cu, const int* __restrict__ slots, int S, const float* __restrict__ bias) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)S * C) return;
   const int s = (int)(idx / C), c = (int)(idx - (long long)s * C);
   const int t0 = cu[s], n = cu[s + 1] - cu[s];
   float* tl = tail + ((long long)slots[s] * C + c) * (K - 1);
+  const float b = bias != nullptr ? bias[c] : 0.f;
   for (int j = 0; j < K - 1; ++j) {
     const int src = n - (K - 1) + j;         // index in the portion of the input that lands in tail[j]
-    tl[j] = src >= 0 ? proj[(long long)(t0 + src) * ldp + c] : tl[j + n];
+    tl[j] = src >= 0 ? proj[(long long)(t0 + src) * ldp + c] + b : tl[j + n];
   }
 }
 
 // One block per (sequence, head); thread j owns column j of the head's state S [dk][dv] (kept in shared memory for the portion).
 // conv [T, C] = silu(conv(q | k | v)); proj holds the gate (g_off), the decay input (a_off) and the write-strength input (b_off).
+// ch 0: one decay per (token, head), from a[t, h] and dt_bias[h].  ch 1: one per (token, head, key channel), from a[t, h dk + i] and
+// dt_bias[h dk + i]; it multiplies the rows of the state.  gate_act 0: silu(gate), 1: sigmoid(gate).
 constexpr int kDeltaTile = 16;
-__global__ void __launch_bounds__(1024) delta_rule_kernel(const float* __restrict__ conv, int C, const float* __restrict__ proj,
-                                                          long long ldp, int g_off, int a_off, int b_off, int H, int Hk, int dk, int dv,
-                                                          const float* __restrict__ A_log, const float* __restrict__ dt_bias,
-                                                          const float* __restrict__ norm_w, float eps, float* __restrict__ state,
-                                                          const int* __restrict__ cu, const int* __restrict__ slots,
-                                                          void* __restrict__ out, int dt_out) {
+__global__ void __launch_bounds__(1024) delta_rule_kernel(const float* __restrict__ conv, int C, const float* __restrict__ bproj,
+                                                          long long ldb, const float* __restrict__ aproj, long long lda, int ch,
+                                                          const float* __restrict__ gproj, long long ldg, int gate_act, int H, int Hk,
+                                                          int dk, int dv, const float* __restrict__ A_log,
+                                                          const float* __restrict__ dt_bias, const float* __restrict__ norm_w, float eps,
+                                                          float* __restrict__ state, const int* __restrict__ cu,
+                                                          const int* __restrict__ slots, void* __restrict__ out, int dt_out) {
   extern __shared__ float sm[];
   float* S = sm;                                  // [dk][dv]
   float* qn = S + (long long)dk * dv;             // [tile][dk]
   float* kn = qn + kDeltaTile * dk;               // [tile][dk]
   float* ob = kn + kDeltaTile * dk;               // [tile][dv]
   float* beta = ob + kDeltaTile * dv;             // [tile]
-  float* dec = beta + kDeltaTile;                 // [tile]
+  float* dec = beta + kDeltaTile;                 // [tile] or [tile][dk]
+  const int dstr = ch ? dk : 1;
   const int s = blockIdx.x, h = blockIdx.y, hk = h / (H / Hk);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
   const int t0 = cu[s], n = cu[s + 1] - cu[s];
   float* Sg = state + ((long long)slots[s] * H + h) * dk * dv;
   for (int i = tid; i < dk * dv; i += blockDim.x) S[i] = Sg[i];
-  const float a_log_h = A_log[h], bias = dt_bias[h], qscale = 1.f / sqrtf((float)dk);
+  const float a_log_h = A_log[h], qscale = 1.f / sqrtf((float)dk);
   const int q_col = hk * dk, k_col = Hk * dk + hk * dk, v_col = 2 * Hk * dk + h * dv;
   for (int b0 = 0; b0 < n; b0 += kDeltaTile) {
     const int nt = min(kDeltaTile, n - b0);
@@ -647,21 +680,19 @@ __global__ void __launch_bounds__(1024) delta_rule_kernel(const float* __restric
         qn[tt * dk + i] = row[q_col + i] * rq;
         kn[tt * dk + i] = row[k_col + i] * rk;
       }
-      if (lane == 0) {
-        const float* pr = proj + (long long)(t0 + b0 + tt) * ldp;
-        beta[tt] = 1.f / (1.f + expf(-pr[b_off + h]));
-        dec[tt] = decay_of(a_log_h, pr[a_off + h], bias);
-      }
+      const float* ar = aproj + (long long)(t0 + b0 + tt) * lda + (long long)h * dstr;
+      for (int i = lane; i < dstr; i += 32) dec[tt * dstr + i] = decay_of(a_log_h, ar[i], dt_bias[h * dstr + i]);
+      if (lane == 0) beta[tt] = 1.f / (1.f + expf(-bproj[(long long)(t0 + b0 + tt) * ldb + h]));
     }
     __syncthreads();
     if (tid < dv) {
       for (int tt = 0; tt < nt; ++tt) {
-        const float g = dec[tt];
+        const float* gg = dec + tt * dstr;
         const float* kk = kn + tt * dk;
         const float* qq = qn + tt * dk;
         float sk = 0.f;
         for (int i = 0; i < dk; ++i) {
-          const float sv = S[i * dv + tid] * g;
+          const float sv = S[i * dv + tid] * gg[ch ? i : 0];
           S[i * dv + tid] = sv;
           sk = fmaf(sv, kk[i], sk);
         }
@@ -682,8 +713,10 @@ __global__ void __launch_bounds__(1024) delta_rule_kernel(const float* __restric
       ss = warp_sum(ss);
       const float rstd = 1.f / sqrtf(ss / (float)dv + eps);
       const long long t = t0 + b0 + tt;
-      for (int j = lane; j < dv; j += 32)
-        st_dt(out, dt_out, (t * H + h) * dv + j, ob[tt * dv + j] * rstd * norm_w[j] * silu(proj[t * ldp + g_off + h * dv + j]));
+      for (int j = lane; j < dv; j += 32) {
+        const float gz = gproj[t * ldg + h * dv + j];
+        st_dt(out, dt_out, (t * H + h) * dv + j, ob[tt * dv + j] * rstd * norm_w[j] * (gate_act ? 1.f / (1.f + expf(-gz)) : silu(gz)));
+      }
     }
   }
   __syncthreads();
@@ -697,11 +730,11 @@ __global__ void __launch_bounds__(1024) delta_rule_kernel(const float* __restric
 // the state in registers, so the k and q values a warp needs are the same for all its lanes (one shared-memory transaction per 16
 // bytes); the pieces of S^T k meet through shared memory and one block barrier per token, those of S^T q once per 8 tokens; q / k / v /
 // gates of the next 8 tokens stream into shared memory with cp.async while the current 8 are processed.  delta_out: per-head RMS norm and SiLU gate.
-__global__ void __launch_bounds__(256) delta_prep_kernel(const float* __restrict__ conv, int C, const float* __restrict__ proj,
-                                                         long long ldp, int a_off, int b_off, int H, int Hk, int dk,
-                                                         const float* __restrict__ A_log, const float* __restrict__ dt_bias, long long T,
-                                                         float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ beta,
-                                                         float* __restrict__ dec) {
+__global__ void __launch_bounds__(256) delta_prep_kernel(const float* __restrict__ conv, int C, const float* __restrict__ bproj,
+                                                         long long ldb, const float* __restrict__ aproj, long long lda, int ch, int H,
+                                                         int Hk, int dk, const float* __restrict__ A_log,
+                                                         const float* __restrict__ dt_bias, long long T, float* __restrict__ qn,
+                                                         float* __restrict__ kn, float* __restrict__ beta, float* __restrict__ dec) {
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (w >= T * Hk) return;
@@ -725,10 +758,14 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(const float* __restrict
   const int rep = H / Hk;
   for (int j = lane; j < rep; j += 32) {
     const int h = hk * rep + j;
-    const float* pr = proj + t * ldp;
-    beta[t * H + h] = 1.f / (1.f + expf(-pr[b_off + h]));
-    dec[t * H + h] = decay_of(A_log[h], pr[a_off + h], dt_bias[h]);
+    beta[t * H + h] = 1.f / (1.f + expf(-bproj[t * ldb + h]));
+    if (!ch) dec[t * H + h] = decay_of(A_log[h], aproj[t * lda + h], dt_bias[h]);
   }
+  if (ch)                                    // one decay per key channel of each of this key head's heads: dec [T][H][dk]
+    for (int e = lane; e < rep * dk; e += 32) {
+      const long long c = (long long)hk * rep * dk + e;
+      dec[t * H * dk + c] = decay_of(A_log[c / dk], aproj[t * lda + c], dt_bias[c]);
+    }
 }
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
@@ -742,7 +779,7 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 
 constexpr int kRegTile = 8;
 constexpr int kRegPieces = 8;                // warps of a block (the sum of the pieces below is written for 8): warp p holds rows [p DK/8, (p+1) DK/8) of 32 state columns
-template <int DK>
+template <int DK, bool CH>
 __global__ void __launch_bounds__(32 * kRegPieces) delta_rule_reg_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
                                                                          const float* __restrict__ conv, int C, int v_col0,
                                                                          const float* __restrict__ beta, const float* __restrict__ dec,
@@ -755,6 +792,7 @@ __global__ void __launch_bounds__(32 * kRegPieces) delta_rule_reg_kernel(const f
   __shared__ __align__(16) float qs[2][kRegTile][DK];
   __shared__ __align__(16) float vs[2][kRegTile][32];
   __shared__ float bs[2][kRegTile], gs[2][kRegTile];
+  __shared__ __align__(16) float gc[CH ? 2 : 1][CH ? kRegTile : 1][CH ? DK : 4];   // per-channel decays of the tile's tokens
   __shared__ float part[2][P][32];          // per token: the pieces of S^T k, summed by every warp after one barrier
   __shared__ float os_part[kRegTile][P][32];   // pieces of S^T q, summed once per tile
   const int s = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * 32;
@@ -773,6 +811,7 @@ __global__ void __launch_bounds__(32 * kRegPieces) delta_rule_reg_kernel(const f
       const long long src = ((long long)(t0 + b0 + tt) * Hk + hk) * DK + cc * 4;
       cp_async16(&ks[buf][tt][cc * 4], kn + src);
       cp_async16(&qs[buf][tt][cc * 4], qn + src);
+      if (CH) cp_async16(&gc[CH ? buf : 0][CH ? tt : 0][cc * 4], dec + ((long long)(t0 + b0 + tt) * H + h) * DK + cc * 4);
     }
     for (int c = tid; c < nt * 8; c += NT) {
       const int tt = c >> 3, cc = c & 7;
@@ -780,7 +819,7 @@ __global__ void __launch_bounds__(32 * kRegPieces) delta_rule_reg_kernel(const f
     }
     if (tid < nt) {
       cp_async4(&bs[buf][tid], beta + (long long)(t0 + b0 + tid) * H + h);
-      cp_async4(&gs[buf][tid], dec + (long long)(t0 + b0 + tid) * H + h);
+      if (!CH) cp_async4(&gs[buf][tid], dec + (long long)(t0 + b0 + tid) * H + h);
     }
     cp_async_commit();
   };
@@ -793,7 +832,7 @@ __global__ void __launch_bounds__(32 * kRegPieces) delta_rule_reg_kernel(const f
     __syncthreads();                                  // tile `buf` is in place; everyone is done with the other buffer and with os_part
     if (b0 + kRegTile < n) load_tile(buf ^ 1, b0 + kRegTile);
     for (int tt = 0; tt < nt; ++tt) {
-      const float g = gs[buf][tt], b = bs[buf][tt];
+      const float g = CH ? 1.f : gs[buf][tt], b = bs[buf][tt];
       // the same address for every lane: one shared-memory transaction per 16 bytes.  All of the token's k and q values are fetched
       // up front (the loads are in flight together, none has to wait behind the barrier below)
       const float4* k4 = reinterpret_cast<const float4*>(&ks[buf][tt][piece * Q]);
@@ -805,6 +844,17 @@ __global__ void __launch_bounds__(32 * kRegPieces) delta_rule_reg_kernel(const f
       for (int ii = 0; ii < Q / 4; ++ii) qr[ii] = q4[ii];
       const float vv = vs[buf][tt][lane];
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      if (CH) {                               // the rows of the state decay each by its own factor before anything reads them
+        const float4* g4 = reinterpret_cast<const float4*>(&gc[CH ? buf : 0][CH ? tt : 0][piece * Q]);
+#pragma unroll
+        for (int ii = 0; ii < Q / 4; ++ii) {
+          const float4 gr = g4[ii];
+          S[4 * ii] *= gr.x;
+          S[4 * ii + 1] *= gr.y;
+          S[4 * ii + 2] *= gr.z;
+          S[4 * ii + 3] *= gr.w;
+        }
+      }
 #pragma unroll
       for (int ii = 0; ii < Q / 4; ++ii) {
         a0 = fmaf(S[4 * ii], kr[ii].x, a0);
@@ -846,10 +896,10 @@ __global__ void __launch_bounds__(32 * kRegPieces) delta_rule_reg_kernel(const f
   for (int ii = 0; ii < Q; ++ii) Sg[(long long)(piece * Q + ii) * dv + j0 + lane] = S[ii];
 }
 
-// out[t, h, :] = o / rms(o) * norm_w * silu(gate); a warp per (token, head)
-__global__ void __launch_bounds__(256) delta_out_kernel(const float* __restrict__ o, const float* __restrict__ proj, long long ldp, int g_off,
-                                                        int H, int dv, const float* __restrict__ norm_w, float eps, long long T,
-                                                        void* __restrict__ out, int dt_out) {
+// out[t, h, :] = o / rms(o) * norm_w * silu(gate) (gate_act 1: sigmoid(gate)); a warp per (token, head)
+__global__ void __launch_bounds__(256) delta_out_kernel(const float* __restrict__ o, const float* __restrict__ gproj, long long ldg,
+                                                        int gate_act, int H, int dv, const float* __restrict__ norm_w, float eps,
+                                                        long long T, void* __restrict__ out, int dt_out) {
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (w >= T * H) return;
@@ -860,8 +910,10 @@ __global__ void __launch_bounds__(256) delta_out_kernel(const float* __restrict_
   for (int j = lane; j < dv; j += 32) ss += row[j] * row[j];
   ss = warp_sum(ss);
   const float rstd = 1.f / sqrtf(ss / (float)dv + eps);
-  for (int j = lane; j < dv; j += 32)
-    st_dt(out, dt_out, w * dv + j, row[j] * rstd * norm_w[j] * silu(proj[t * ldp + g_off + h * dv + j]));
+  for (int j = lane; j < dv; j += 32) {
+    const float gz = gproj[t * ldg + h * dv + j];
+    st_dt(out, dt_out, w * dv + j, row[j] * rstd * norm_w[j] * (gate_act ? 1.f / (1.f + expf(-gz)) : silu(gz)));
+  }
 }
 
 }  // namespace kb2seq
@@ -993,18 +1045,84 @@ KB2SEQ_API int kb2_seq_latent_window_attn(const float* q_abs, const float* proj,
   return KB2SEQ_OK;
 }
 
-KB2SEQ_API int kb2_seq_conv_silu(const float* proj, long long ldp, int T, int S, int C, int K, const float* taps, float* tail,
-                                 const int* seq_of, const int* cu, const int* slots, float* out, void* stream) {
-  if (!proj || !taps || !tail || !seq_of || !cu || !slots || !out || T <= 0 || S <= 0 || C <= 0 || K <= 0)
-    return failf(KB2SEQ_ERR_VALUE, "conv_silu: bad argument");
-  if (T > 65535) return failf(KB2SEQ_ERR_VALUE, "conv_silu: more than 65535 rows in one step");
-  conv_silu_kernel<<<dim3((C + 255) / 256, T), 256, 0, (cudaStream_t)stream>>>(proj, ldp, C, K, taps, tail, seq_of, cu, slots, T, out);
+KB2SEQ_API int kb2_seq_conv(const float* proj, long long ldp, int T, int S, int C, int K, const float* taps, const float* bias, int act,
+                            float* tail, const int* seq_of, const int* cu, const int* slots, float* out, void* stream) {
+  if (!proj || !taps || !tail || !seq_of || !cu || !slots || !out || T <= 0 || S <= 0 || C <= 0 || K <= 0 || act < 0 || act > 1)
+    return failf(KB2SEQ_ERR_VALUE, "conv: bad argument");
+  if (T > 65535) return failf(KB2SEQ_ERR_VALUE, "conv: more than 65535 rows in one step");
+  conv_silu_kernel<<<dim3((C + 255) / 256, T), 256, 0, (cudaStream_t)stream>>>(proj, ldp, C, K, taps, tail, seq_of, cu, slots, T, out, bias,
+                                                                               act);
   SEQ_LAUNCHED();
   if (K > 1) {
     const long long m = (long long)S * C;
-    conv_tail_kernel<<<(unsigned)((m + 255) / 256), 256, 0, (cudaStream_t)stream>>>(proj, ldp, C, K, tail, cu, slots, S);
+    conv_tail_kernel<<<(unsigned)((m + 255) / 256), 256, 0, (cudaStream_t)stream>>>(proj, ldp, C, K, tail, cu, slots, S, bias);
     SEQ_LAUNCHED();
   }
+  return KB2SEQ_OK;
+}
+
+KB2SEQ_API int kb2_seq_conv_silu(const float* proj, long long ldp, int T, int S, int C, int K, const float* taps, float* tail,
+                                 const int* seq_of, const int* cu, const int* slots, float* out, void* stream) {
+  return kb2_seq_conv(proj, ldp, T, S, C, K, taps, nullptr, 1, tail, seq_of, cu, slots, out, stream);
+}
+
+KB2SEQ_API int kb2_seq_residual_scale_rms(float* x, const float* y, float y_mult, const float* w, float w_shift, void* h, int dt_h, int T,
+                                          int W, float eps, void* stream) {
+  if (!x || T <= 0 || W <= 0 || bad_dt(dt_h) || (h && !w)) return failf(KB2SEQ_ERR_VALUE, "residual_scale_rms: bad argument");
+  if (h == (void*)x && (y || dt_h != 0)) return failf(KB2SEQ_ERR_VALUE, "residual_scale_rms: a norm in place takes no addend and is fp32");
+  const size_t smem = (size_t)W * 4;
+  if (smem > 200 * 1024) return failf(KB2SEQ_ERR_VALUE, "residual_scale_rms: width %d too large", W);
+  if (smem > 48 * 1024) SEQ_CUDA(cudaFuncSetAttribute(residual_scale_rms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  residual_scale_rms_kernel<<<T, 256, smem, (cudaStream_t)stream>>>(x, y, y_mult, w, w_shift, h, dt_h, W, eps);
+  SEQ_LAUNCHED();
+  return KB2SEQ_OK;
+}
+
+static int delta_rule_launch(const float* conv, int C, const float* bproj, long long ldb, const float* aproj, long long lda, int ch,
+                             const float* gproj, long long ldg, int gate_act, int T, int S, int H, int Hk, int dk, int dv,
+                             const float* A_log, const float* dt_bias, const float* norm_w, float eps, float* state, const int* cu,
+                             const int* slots, float* scratch, void* out, int dt_out, void* stream) {
+  if (!conv || !bproj || !aproj || !gproj || !A_log || !dt_bias || !norm_w || !state || !cu || !slots || !out || S <= 0 || H <= 0 ||
+      Hk <= 0 || H % Hk || dk <= 0 || dv <= 0 || bad_dt(dt_out))
+    return failf(KB2SEQ_ERR_VALUE, "delta_rule: bad argument");
+  if (scratch && (dk == 32 || dk == 64 || dk == 128) && dv % 32 == 0 && C % 4 == 0 && ((2 * Hk * dk) % 4) == 0) {
+    // scratch: qn [T, Hk, dk] | kn [T, Hk, dk] | beta [T, H] | dec [T, H] or [T, H, dk] | o [T, H, dv]   (fp32)
+    cudaStream_t st = (cudaStream_t)stream;
+    float* qn = scratch;
+    float* kn = qn + (long long)T * Hk * dk;
+    float* be = kn + (long long)T * Hk * dk;
+    float* de = be + (long long)T * H;
+    if (ch) de = (float*)(((uintptr_t)de + 15) & ~(uintptr_t)15);
+    float* ob = de + (long long)T * H * (ch ? dk : 1);
+    ob = (float*)(((uintptr_t)ob + 15) & ~(uintptr_t)15);
+    const long long nw = (long long)T * Hk;
+    delta_prep_kernel<<<(unsigned)((nw + 7) / 8), 256, 0, st>>>(conv, C, bproj, ldb, aproj, lda, ch, H, Hk, dk, A_log, dt_bias, T, qn, kn, be, de);
+    SEQ_LAUNCHED();
+    dim3 grid(S, H, dv / 32);
+    const int v_col0 = 2 * Hk * dk;
+#define R(DK, CHV) delta_rule_reg_kernel<DK, CHV><<<grid, 32 * kRegPieces, 0, st>>>(qn, kn, conv, C, v_col0, be, de, H, Hk, dv, state, cu, slots, ob)
+    if (ch) {
+      if (dk == 32) R(32, true); else if (dk == 64) R(64, true); else R(128, true);
+    } else {
+      if (dk == 32) R(32, false); else if (dk == 64) R(64, false); else R(128, false);
+    }
+#undef R
+    SEQ_LAUNCHED();
+    const long long no = (long long)T * H;
+    delta_out_kernel<<<(unsigned)((no + 7) / 8), 256, 0, st>>>(ob, gproj, ldg, gate_act, H, dv, norm_w, eps, T, out, dt_out);
+    SEQ_LAUNCHED();
+    return KB2SEQ_OK;
+  }
+  if (dv > 1024) return failf(KB2SEQ_ERR_VALUE, "delta_rule: value size %d > 1024", dv);
+  const size_t smem = ((size_t)dk * dv + (size_t)kDeltaTile * (2 * dk + dv + 1 + (ch ? dk : 1))) * 4;
+  if (smem > 220 * 1024) return failf(KB2SEQ_ERR_VALUE, "delta_rule: a %d x %d state does not fit one block's shared memory", dk, dv);
+  if (smem > 48 * 1024) SEQ_CUDA(cudaFuncSetAttribute(delta_rule_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int threads = (dv + 31) / 32 * 32;
+  if (threads < 128) threads = 128;
+  dim3 grid(S, H);
+  delta_rule_kernel<<<grid, threads, smem, (cudaStream_t)stream>>>(conv, C, bproj, ldb, aproj, lda, ch, gproj, ldg, gate_act, H, Hk, dk, dv, A_log,
+                                                                  dt_bias, norm_w, eps, state, cu, slots, out, dt_out);
+  SEQ_LAUNCHED();
   return KB2SEQ_OK;
 }
 
@@ -1012,43 +1130,18 @@ KB2SEQ_API int kb2_seq_delta_rule(const float* conv, int C, const float* proj, l
                                   int S, int H, int Hk, int dk, int dv, const float* A_log, const float* dt_bias, const float* norm_w,
                                   float eps, float* state, const int* cu, const int* slots, float* scratch, void* out, int dt_out,
                                   void* stream) {
-  if (!conv || !proj || !A_log || !dt_bias || !norm_w || !state || !cu || !slots || !out || S <= 0 || H <= 0 || Hk <= 0 || H % Hk ||
-      dk <= 0 || dv <= 0 || bad_dt(dt_out))
-    return failf(KB2SEQ_ERR_VALUE, "delta_rule: bad argument");
-  if (scratch && (dk == 32 || dk == 64 || dk == 128) && dv % 32 == 0 && C % 4 == 0 && ((2 * Hk * dk) % 4) == 0) {
-    // scratch: qn [T, Hk, dk] | kn [T, Hk, dk] | beta [T, H] | dec [T, H] | o [T, H, dv]   (fp32)
-    cudaStream_t st = (cudaStream_t)stream;
-    float* qn = scratch;
-    float* kn = qn + (long long)T * Hk * dk;
-    float* be = kn + (long long)T * Hk * dk;
-    float* de = be + (long long)T * H;
-    float* ob = de + (long long)T * H;
-    if ((((long long)T * Hk * dk) | ((long long)T * H)) % 4) ob = (float*)(((uintptr_t)ob + 15) & ~(uintptr_t)15);
-    const long long nw = (long long)T * Hk;
-    delta_prep_kernel<<<(unsigned)((nw + 7) / 8), 256, 0, st>>>(conv, C, proj, ldp, a_off, b_off, H, Hk, dk, A_log, dt_bias, T, qn, kn, be, de);
-    SEQ_LAUNCHED();
-    dim3 grid(S, H, dv / 32);
-    const int v_col0 = 2 * Hk * dk;
-    if (dk == 32) delta_rule_reg_kernel<32><<<grid, 32 * kRegPieces, 0, st>>>(qn, kn, conv, C, v_col0, be, de, H, Hk, dv, state, cu, slots, ob);
-    else if (dk == 64) delta_rule_reg_kernel<64><<<grid, 32 * kRegPieces, 0, st>>>(qn, kn, conv, C, v_col0, be, de, H, Hk, dv, state, cu, slots, ob);
-    else delta_rule_reg_kernel<128><<<grid, 32 * kRegPieces, 0, st>>>(qn, kn, conv, C, v_col0, be, de, H, Hk, dv, state, cu, slots, ob);
-    SEQ_LAUNCHED();
-    const long long no = (long long)T * H;
-    delta_out_kernel<<<(unsigned)((no + 7) / 8), 256, 0, st>>>(ob, proj, ldp, g_off, H, dv, norm_w, eps, T, out, dt_out);
-    SEQ_LAUNCHED();
-    return KB2SEQ_OK;
-  }
-  if (dv > 1024) return failf(KB2SEQ_ERR_VALUE, "delta_rule: value size %d > 1024", dv);
-  const size_t smem = ((size_t)dk * dv + (size_t)kDeltaTile * (2 * dk + dv + 2)) * 4;
-  if (smem > 220 * 1024) return failf(KB2SEQ_ERR_VALUE, "delta_rule: a %d x %d state does not fit one block's shared memory", dk, dv);
-  if (smem > 48 * 1024) SEQ_CUDA(cudaFuncSetAttribute(delta_rule_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  int threads = (dv + 31) / 32 * 32;
-  if (threads < 128) threads = 128;
-  dim3 grid(S, H);
-  delta_rule_kernel<<<grid, threads, smem, (cudaStream_t)stream>>>(conv, C, proj, ldp, g_off, a_off, b_off, H, Hk, dk, dv, A_log, dt_bias, norm_w,
-                                                                  eps, state, cu, slots, out, dt_out);
-  SEQ_LAUNCHED();
-  return KB2SEQ_OK;
+  if (!proj) return failf(KB2SEQ_ERR_VALUE, "delta_rule: bad argument");
+  return delta_rule_launch(conv, C, proj + b_off, ldp, proj + a_off, ldp, 0, proj + g_off, ldp, 0, T, S, H, Hk, dk, dv, A_log, dt_bias, norm_w,
+                           eps, state, cu, slots, scratch, out, dt_out, stream);
+}
+
+KB2SEQ_API int kb2_seq_delta_rule_ch(const float* conv, int C, const float* beta_in, long long ldb, const float* decay_in, long long lda,
+                                     const float* gate_in, long long ldg, int gate_act, int T, int S, int H, int Hk, int dk, int dv,
+                                     const float* A_log, const float* dt_bias, const float* norm_w, float eps, float* state, const int* cu,
+                                     const int* slots, float* scratch, void* out, int dt_out, void* stream) {
+  if (gate_act < 0 || gate_act > 1) return failf(KB2SEQ_ERR_VALUE, "delta_rule_ch: bad argument");
+  return delta_rule_launch(conv, C, beta_in, ldb, decay_in, lda, 1, gate_in, ldg, gate_act, T, S, H, Hk, dk, dv, A_log, dt_bias, norm_w, eps,
+                           state, cu, slots, scratch, out, dt_out, stream);
 }
 
 }  // extern "C"

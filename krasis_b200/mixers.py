@@ -12,9 +12,16 @@ libkrasis_b200_seq (`krasis_b200.seqops`): a model composes them (krasis_b200/vo
                           query / key RMS norm, interleaved rotary positions on part of the dimensions with linear scaling, a causal
                           mask cut into chunks and / or a sliding window, a unit norm per head, a per-head sigmoid output gate, and
                           optionally another layer's cached keys and values instead of projections of its own
-  GatedMLP                down(act(gate h) * (up h)): tanh-GELU, SiLU, or the clamped swish form g' sigmoid(a g') (u' + 1)
-  RoutedExperts           softmax / sigmoid router with a choice correction, expert groups and identity experts, top-k SiLU experts
-                          (binned tile GEMMs; a GEMV form for steps of few tokens) plus an optional shared expert
+                          (further options: a short causal convolution on q / k / v after the projection, one RMS norm over the whole
+                          of q and of k, rotation of dimension i with i + dims / 2, a frequency table of the caller, tanh soft-capped
+                          scores)
+  ChannelDeltaMixer       the gated delta rule with one decay per head and key channel (low-rank decay and output-gate projections,
+                          sigmoid output gate)
+  GatedMLP                down(act(gate h) * (up h)): tanh-GELU, SiLU, or the clamped swish form g' sigmoid(a g') (u' + 1); without a
+                          gate: down(relu(up h)^2)
+  RoutedExperts           softmax / sigmoid router with a choice correction, expert groups (scored by their best or their two best
+                          outputs) and identity experts, top-k experts of either form (binned tile GEMMs; a GEMV form for steps of few
+                          tokens) plus an optional shared expert with an optional per-token sigmoid gate
   TokenSideInput          per-layer token table slice, gated by a projection of the residual stream, RMS-normed
 `lin(a, w, out_dtype)` picks the GEMM: the tcgen05 kernel of the core library for large aligned bf16 products, the generic
 kernel of the sequence library otherwise (any shape, fp32 or bf16).
@@ -196,15 +203,79 @@ class GatedDeltaMixer:
         return lin(o, self.w_o, torch.float32)
 
 
+class ChannelDeltaMixer:
+    """Gated delta rule whose decay is one number per head and key channel.
+    weights: q, k [Hk dk, W], v [H dv, W], b [H, W], a1 [r, W], a2 [H dk, r], g1 [r', W], g2 [H dv, r'], q_conv, k_conv, v_conv
+    [channels, taps], A_log [H], dt_bias [H dk], norm [dv], o [W, H dv].
+
+    Per token: q, k, v = silu(conv(projection)); q and k unit vectors per head (q also times dk^-1/2); beta = sigmoid(b h);
+    g = exp(-exp(A_log[h]) softplus(a2 (a1 h) + dt_bias)) per (head, key channel); S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T;
+    o = S^T q; out = o / rms(o) * norm * sigmoid(g2 (g1 h)), then the output projection.  State and everything that feeds the recurrence
+    are fp32."""
+
+    def __init__(self, weights: dict, heads: int, kv_heads: int, dim: int, vdim: int, taps: int, eps: float, dtype, device):
+        self.H, self.Hk, self.dk, self.dv, self.K = heads, kv_heads, dim, vdim, int(taps)
+        if heads % kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.eps, self.dtype, self.device = float(eps), dtype, device
+        d = lambda t: t.to(device=device, dtype=dtype).contiguous()
+        f = lambda t: t.to(device=device, dtype=torch.float32).contiguous()
+        self.C = 2 * kv_heads * dim + heads * vdim                                  # convolved channels: q | k | v
+        self.ra, self.rg = weights["a1"].shape[0], weights["g1"].shape[0]
+        self.b_off, self.a_off, self.g_off = self.C, self.C + heads, self.C + heads + self.ra
+        self.w_in = d(torch.cat([weights[k] for k in ("q", "k", "v", "b", "a1", "g1")], 0))     # one projection of the layer input
+        self.w_a2, self.w_g2 = d(weights["a2"]), d(weights["g2"])
+        self.taps = f(torch.cat([weights["q_conv"], weights["k_conv"], weights["v_conv"]], 0))
+        self.A_log, self.dt_bias, self.norm = f(weights["A_log"]), f(weights["dt_bias"]), f(weights["norm"])
+        if self.dt_bias.numel() != heads * dim or self.w_a2.shape[0] != heads * dim or self.w_g2.shape[0] != heads * vdim:
+            raise ValueError("decay / gate projections do not match heads x dim / heads x vdim")
+        self.w_o = d(weights["o"])
+        self.register_state_kernel = dim in (32, 64, 128) and vdim % 32 == 0
+
+    def register_state(self, pool):
+        """(conv tail [slots, C, taps - 1], recurrent state [slots, H, dk, dv]) in a RecurrentStatePool."""
+        return pool.register(self.C, max(self.K - 1, 1)), pool.register(self.H, self.dk, self.dv)
+
+    def _second(self, proj, off, r, w):
+        a = proj[:, off:off + r]
+        if self.dtype == torch.bfloat16:
+            a = a.to(torch.bfloat16)
+        return lin(a.contiguous(), w, torch.float32)
+
+    def forward(self, h: torch.Tensor, tb: ops.StepTables, tail: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
+        lib, T, H = ops.load(), h.shape[0], self.H
+        proj = lin(h, self.w_in, torch.float32)
+        s = torch.cuda.current_stream(h.device).cuda_stream
+        conv = ops.conv(proj, self.C, self.taps, None, True, tail, tb)
+        dec_in = self._second(proj, self.a_off, self.ra, self.w_a2)                 # [T, H dk]
+        gate_in = self._second(proj, self.g_off, self.rg, self.w_g2)                # [T, H dv]
+        o = torch.empty((T, H * self.dv), dtype=self.dtype, device=h.device)
+        scratch = None
+        if self.register_state_kernel:
+            n = 2 * T * self.Hk * self.dk + T * H + T * H * self.dk + T * H * self.dv + 16
+            scratch = torch.empty(n, dtype=torch.float32, device=h.device)
+        beta_in = proj[:, self.b_off:]
+        ops.check(lib.kb2_seq_delta_rule_ch(conv.data_ptr(), self.C, beta_in.data_ptr(), proj.stride(0), dec_in.data_ptr(), dec_in.stride(0),
+                                            gate_in.data_ptr(), gate_in.stride(0), 1, T, tb.S, H, self.Hk, self.dk, self.dv,
+                                            self.A_log.data_ptr(), self.dt_bias.data_ptr(), self.norm.data_ptr(), self.eps,
+                                            state.data_ptr(), tb.cu.data_ptr(), tb.slots.data_ptr(), ops._ptr(scratch), o.data_ptr(),
+                                            ops.dt_code(self.dtype), s))
+        return lin(o, self.w_o, torch.float32)
+
+
 class GatedMLP:
     """weights: gate, up [F, W], down [W, F].  act: "gelu_tanh" (gelu(g) u), "silu" (silu(g) u) or "clamped_swish"
-    (g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit))."""
+    (g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)).  gated False: weights up, down only and
+    down(act(up h)) with act "relu2" (the square of relu)."""
 
-    KINDS = {"gelu_tanh": ops.GLU_GELU_TANH, "silu": ops.GLU_SILU, "clamped_swish": ops.GLU_CLAMPED_SWISH}
+    KINDS = {"gelu_tanh": ops.GLU_GELU_TANH, "silu": ops.GLU_SILU, "clamped_swish": ops.GLU_CLAMPED_SWISH, "relu2": ops.ACT_RELU2}
 
-    def __init__(self, weights: dict, dtype, device, act: str = "gelu_tanh", limit: float = 0.0, alpha: float = 1.0):
+    def __init__(self, weights: dict, dtype, device, act: str = "gelu_tanh", limit: float = 0.0, alpha: float = 1.0, gated: bool = True):
         d = lambda t: t.to(device=device, dtype=dtype).contiguous()
-        self.w_gu, self.w_down, self.dtype = d(torch.cat([weights["gate"], weights["up"]], 0)), d(weights["down"]), dtype
+        if gated == (act == "relu2"):
+            raise ValueError("relu2 is the activation of the ungated form, and its only one")
+        self.w_gu = d(torch.cat([weights["gate"], weights["up"]], 0)) if gated else d(weights["up"])
+        self.w_down, self.dtype = d(weights["down"]), dtype
         self.kind, self.limit, self.alpha = self.KINDS[act], float(limit), float(alpha)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
@@ -219,6 +290,23 @@ def rotary_table(dims: int, base: float, factor: float = 1.0) -> torch.Tensor:
     return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims) / float(factor)
 
 
+def llama3_table(dims: int, base: float, scaling=None) -> torch.Tensor:
+    """Angular frequency of each rotated pair (fp64), base^(-2i / dims), rescaled by wavelength l = 2 pi / f against a training length
+    `original`: kept where l < original / high, divided by `factor` where l > original / low, and in between blended as
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low).  scaling = {factor, low, high, original} or None."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
+    if not scaling:
+        return f
+    factor, low, high, orig = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+    wave = 2.0 * math.pi / f
+    if high == low:
+        return torch.where(wave > orig / low, f / factor, f)
+    sm = (orig / wave - low) / (high - low)
+    mid = (1.0 - sm) * f / factor + sm * f
+    return torch.where(wave < orig / high, f, torch.where(wave > orig / low, f / factor, mid))
+
+
 class MultiMapAttention:
     """weights: q [H M d, W], k [G M d, W], v [G dv, W] (each with an optional bias `<name>_b`), q_norm / k_norm [d] (optional RMS norm
     weights, shared by heads and maps), g [H, W] (optional output gate), o [W, H dv].  Rows of q and k are laid out head by head as
@@ -226,11 +314,18 @@ class MultiMapAttention:
 
     A head's output is sum_m map_coef[m] * softmax(q_m k_m^T scale) v over the visible keys (same chunk of `chunk` positions counted
     from position 0, at most `window` back, causal); with unit_norm it is divided by its root mean square and multiplied by
-    post_scale; with a gate it is multiplied by sigmoid(g h)."""
+    post_scale; with a gate it is multiplied by sigmoid(g h).
+
+    conv_taps > 0: q_conv / k_conv / v_conv [channels, taps] — a short causal convolution over time on every channel of the biased
+    projections, ahead of norm and rotation; its last taps - 1 inputs per sequence live in a state slot (`register_state`).
+    norm_whole: q_norm / k_norm have the size of the whole projection and one root mean square is taken over all of q (of k).
+    rot_half: dimension i turns with i + rot_dims / 2 (default: 2i with 2i + 1).  rot_freq: the frequency table, if not
+    base^(-2i / dims) / rot_factor.  softcap > 0: a scaled score s becomes softcap tanh(s / softcap)."""
 
     def __init__(self, weights: dict, heads: int, kv_heads: int, maps: int, dim: int, vdim: int, scale: float, eps: float, dtype, device,
                  chunk=None, window=None, rot_dims: int = 0, rot_base: float = 10000.0, rot_factor: float = 1.0, map_coef=None,
-                 unit_norm: bool = False, post_scale: float = 1.0, own_kv: bool = True):
+                 unit_norm: bool = False, post_scale: float = 1.0, own_kv: bool = True, conv_taps: int = 0, norm_whole: bool = False,
+                 rot_half: bool = False, rot_freq=None, softcap: float = 0.0):
         if heads % kv_heads:
             raise ValueError("heads must be a multiple of kv_heads")
         if rot_dims > dim or rot_dims % 2:
@@ -241,6 +336,13 @@ class MultiMapAttention:
         self.window = int(window) if window else 1 << 30
         self.rot_dims = int(rot_dims)
         self.freq = rotary_table(self.rot_dims, rot_base, rot_factor).to(device) if self.rot_dims else None
+        if self.rot_dims and rot_freq is not None:
+            if rot_freq.numel() != self.rot_dims // 2:
+                raise ValueError("one frequency per rotated pair")
+            self.freq = rot_freq.to(device=device, dtype=torch.float64).contiguous()
+        self.norm_whole, self.rot_half, self.softcap, self.K = bool(norm_whole), bool(rot_half), float(softcap or 0.0), int(conv_taps or 0)
+        if self.K and not own_kv:
+            raise ValueError("the convolution needs projections of the layer's own")
         self.unit_norm, self.post_scale = bool(unit_norm), float(post_scale)
         d = lambda t: t.to(device=device, dtype=dtype).contiguous()
         f = lambda t: t.to(device=device, dtype=torch.float32).contiguous()
@@ -260,6 +362,11 @@ class MultiMapAttention:
         self.q_norm = f(weights["q_norm"]) if "q_norm" in weights else None
         self.k_norm = f(weights["k_norm"]) if (own_kv and "k_norm" in weights) else None
         self.w_o = d(weights["o"])
+        self.C = sum(weights[n].shape[0] for n in names)                    # q | k | v columns of the projection
+        self.taps = f(torch.cat([weights[n + "_conv"] for n in names], 0)) if self.K else None
+        for nm, w, n in (("q", self.q_norm, heads * maps * dim), ("k", self.k_norm, kv_heads * maps * dim)):
+            if w is not None and w.numel() != (n if norm_whole else dim):
+                raise ValueError(f"{nm}_norm has {w.numel()} weights")
         # long prompt portions in bfloat16 with 128 query / key dims per map and 128 or 256 value dims run the tcgen05 attention core of
         # the MoE prefill models, one call per chunk the portion touches, on keys and values gathered from the pages
         self.tc_min_portion = 128
@@ -267,6 +374,10 @@ class MultiMapAttention:
 
     def cache_dims(self):
         return self.G * self.M * self.d, self.G * self.dv
+
+    def register_state(self, pool):
+        """Convolution tail [slots, C, taps - 1] in a RecurrentStatePool (None without a convolution)."""
+        return pool.register(self.C, max(self.K - 1, 1)) if self.K else None
 
     def _tensor_core_portion(self, core, proj, a, tb, i, kc, vc, page_size, stream):
         """Sequence i of the step on the tcgen05 kernel: a[rows of the portion] = per-map attention outputs (fp32)."""
@@ -296,21 +407,24 @@ class MultiMapAttention:
                                           min(self.window, 1 << 30), proj.device.index or 0, stream))
             pos = end
 
-    def forward(self, h: torch.Tensor, tb: ops.StepTables, kc: torch.Tensor, vc: torch.Tensor, page_size: int) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, tb: ops.StepTables, kc: torch.Tensor, vc: torch.Tensor, page_size: int, tail=None) -> torch.Tensor:
         lib, T, H, G, M = ops.load(), h.shape[0], self.H, self.G, self.M
-        proj = lin(h, self.w_in, torch.float32)
+        proj_in = proj = lin(h, self.w_in, torch.float32)
+        bias = self.bias
+        if self.K:                                   # q | k | v through the convolution (bias first); the gate columns stay in proj_in
+            proj, bias = ops.conv(proj_in, self.C, self.taps, self.bias, False, tail, tb), None
         ldp = proj.stride(0)
         s = torch.cuda.current_stream(h.device).cuda_stream
         dtc = ops.dt_code(kc.dtype)
-        ops.check(lib.kb2_seq_head_kv_prep(proj.data_ptr(), ldp, T, H, G if self.own_kv else 0, M, self.d, self.dv, ops._ptr(self.bias),
+        ops.check(lib.kb2_seq_head_kv_prep(proj.data_ptr(), ldp, T, H, G if self.own_kv else 0, M, self.d, self.dv, ops._ptr(bias),
                                            ops._ptr(self.q_norm), ops._ptr(self.k_norm), self.eps, ops._ptr(self.freq), self.rot_dims,
                                            tb.positions.data_ptr(), tb.seq_of.data_ptr(), tb.pages.data_ptr(), tb.max_pages, page_size,
-                                           kc.data_ptr(), vc.data_ptr(), dtc, s))
+                                           kc.data_ptr(), vc.data_ptr(), dtc, int(self.norm_whole), int(self.rot_half), s))
         # a step of few tokens (decoding) cuts each token's keys into pieces so that the whole GPU works on them
         reach = min(self.window, self.chunk) if self.chunk else self.window
         max_keys = max(min(reach, start + n) for _, n, start, _ in tb.layout)
         nsplit = max(1, min(296 // max(T * G, 1), (max_keys + 31) // 32, 64))
-        core = _core_lib() if self.tc_shape else False
+        core = _core_lib() if (self.tc_shape and self.softcap == 0.0) else False
         fast = [i for i, (_, n, _, _) in enumerate(tb.layout) if n >= self.tc_min_portion] if core else []
         if fast:
             nsplit = 1
@@ -325,43 +439,59 @@ class MultiMapAttention:
             ops.check(lib.kb2_seq_paged_attn(proj.data_ptr(), ldp, T, H, G, M, self.d, self.dv, kc.data_ptr(), vc.data_ptr(), dtc,
                                              tb.positions.data_ptr(), tb.seq_of.data_ptr(), tb.pages.data_ptr(), tb.max_pages, page_size,
                                              self.scale, self.chunk, min(self.window, 1 << 30), a.data_ptr(), nsplit, ops._ptr(part_acc),
-                                             ops._ptr(part_ml), tb.cu.data_ptr() if fast else None, self.tc_min_portion, s))
+                                             ops._ptr(part_ml), tb.cu.data_ptr() if fast else None, self.tc_min_portion, self.softcap, s))
         for i in fast:
             self._tensor_core_portion(core, proj, a, tb, i, kc, vc, page_size, s)
         o = torch.empty((T, H * self.dv), dtype=self.dtype, device=h.device)
-        gate = proj[:, self.gate_off:] if self.gate_off >= 0 else None
+        gate = proj_in[:, self.gate_off:] if self.gate_off >= 0 else None
         ops.check(lib.kb2_seq_attn_finish(a.data_ptr(), ops._ptr(part_acc), ops._ptr(part_ml), nsplit, T, H, M, self.dv, ops._ptr(self.map_coef),
-                                          int(self.unit_norm), self.eps, self.post_scale, ops._ptr(gate), ldp, o.data_ptr(),
+                                          int(self.unit_norm), self.eps, self.post_scale, ops._ptr(gate), proj_in.stride(0), o.data_ptr(),
                                           ops.dt_code(self.dtype), None, None, 0, s))
         return lin(o, self.w_o, torch.float32)
 
 
 class RoutedExperts:
     """weights: router [E + identity, W], correction [E + identity] (optional), e<i>_gate / e<i>_up [F, W], e<i>_down [W, F] for i < E,
-    shared_gate / shared_up / shared_down (optional shared expert of the same SiLU form, run for every token and added).
+    shared_gate / shared_up / shared_down (optional shared expert of the same form, run for every token and added), shared_sg [1, W]
+    (optional: the shared expert's output is multiplied by sigmoid(shared_sg h), one number per token).
+    gated False: the experts (and the shared one) have no gate tensor and compute down(act(up h)); act: "silu" (gated) or "relu2".
 
     Scores are softmax (or sigmoid) of the fp32 router logits over all E + identity outputs; the choice adds `correction`; the outputs
-    form `groups` equal groups of neighbours of which the `keep` with the largest maximal choice stay eligible; the `top` largest
-    choices are taken and weighted by their scores (renormalised if `renorm`).  The last `identity` outputs are identity experts:
-    they return their input."""
+    form `groups` equal groups of neighbours of which the `keep` with the largest group score stay eligible (group_score "max": the
+    group's largest choice, "top2": the sum of its two largest); the `top` largest choices are taken and weighted by their scores
+    (divided by their sum if `renorm`, times out_scale).  The last `identity` outputs are identity experts: they return their input."""
 
     def __init__(self, weights: dict, experts: int, identity: int, top: int, dtype, device, groups: int = 1, keep: int = 1,
-                 score: str = "softmax", renorm: bool = False, out_scale: float = 1.0):
+                 score: str = "softmax", renorm: bool = False, out_scale: float = 1.0, gated: bool = True, act: str = "silu",
+                 group_score: str = "max"):
         d = lambda t: t.to(device=device, dtype=dtype).contiguous()
         self.E, self.ident, self.top, self.groups, self.keep = int(experts), int(identity), int(top), int(groups), int(keep)
         self.score, self.renorm, self.out_scale, self.dtype, self.device = score, bool(renorm), float(out_scale), dtype, device
+        self.gated, self.group_score = bool(gated), group_score
+        if gated == (act == "relu2") or act not in ("silu", "relu2") or group_score not in ("max", "top2"):
+            raise ValueError("experts: silu with a gate or relu2 without; group_score max or top2")
+        self.act_kind = ops.GLU_SILU if gated else ops.ACT_RELU2
         if weights["router"].shape[0] != self.E + self.ident:
             raise ValueError("router rows must equal experts + identity experts")
         if (self.E + self.ident) % self.groups or not 1 <= self.keep <= self.groups:
             raise ValueError("expert groups must divide experts + identity experts, 1 <= keep <= groups")
-        self.w_router = d(weights["router"])
+        rows = [weights["router"]]
+        self.sg_col = -1
+        if "shared_sg" in weights:                  # the shared expert's gate rides on the router product as one more column
+            self.sg_col = self.E + self.ident
+            rows.append(weights["shared_sg"].reshape(1, -1))
+            pad = -(self.sg_col + 1) % 16           # a width the tensor-core product takes
+            if pad:
+                rows.append(torch.zeros(pad, weights["router"].shape[1], dtype=weights["router"].dtype))
+        self.w_router = d(torch.cat(rows, 0))
         self.correction = weights["correction"].to(device=device, dtype=torch.float32).contiguous() if "correction" in weights else None
         if self.E:
-            self.w_gu = d(torch.stack([torch.cat([weights[f"e{i}_gate"], weights[f"e{i}_up"]], 0) for i in range(self.E)], 0))   # [E, 2F, W]
-            self.w_down = d(torch.stack([weights[f"e{i}_down"] for i in range(self.E)], 0))                                      # [E, W, F]
+            first = (lambda i: torch.cat([weights[f"e{i}_gate"], weights[f"e{i}_up"]], 0)) if gated else (lambda i: weights[f"e{i}_up"])
+            self.w_gu = d(torch.stack([first(i) for i in range(self.E)], 0))                         # [E, 2F | F, W]
+            self.w_down = d(torch.stack([weights[f"e{i}_down"] for i in range(self.E)], 0))          # [E, W, F]
             self.F = self.w_down.shape[2]
-        self.shared = GatedMLP({k[len("shared_"):]: v for k, v in weights.items() if k.startswith("shared_")}, dtype, device, act="silu") \
-            if "shared_gate" in weights else None
+        self.shared = GatedMLP({k[len("shared_"):]: v for k, v in weights.items() if k.startswith("shared_") and k != "shared_sg"}, dtype,
+                               device, act=act, gated=gated) if "shared_up" in weights else None
         self.tile = ops.load().kb2_seq_moe_tile_rows()
         self.gemv_max_tokens = 8
         # bfloat16 steps that bring at least this many rows per expert on average run on the grouped tcgen05 GEMM (128-row tiles)
@@ -397,23 +527,26 @@ class RoutedExperts:
         rows, di = t["max_rows"], dev.index or 0
         src = torch.div(t["slot_row"].clamp_min(0), top, rounding_mode="floor").to(torch.int64)     # padding rows read token 0; never used
         xs = h.index_select(0, src)
-        gu = torch.empty((rows, 2 * F), dtype=torch.bfloat16, device=dev)
-        capi.check(core.kb2_linear_bf16_grouped(xs.data_ptr(), self.w_gu.data_ptr(), gu.data_ptr(), rows, 2 * F, W, 0, t["tile_expert"].data_ptr(),
+        F1 = self.w_gu.shape[1]
+        gu = torch.empty((rows, F1), dtype=torch.bfloat16, device=dev)
+        capi.check(core.kb2_linear_bf16_grouped(xs.data_ptr(), self.w_gu.data_ptr(), gu.data_ptr(), rows, F1, W, 0, t["tile_expert"].data_ptr(),
                                                 t["n_tiles"].data_ptr(), E, di, s))
-        act = ops.glu(gu, torch.bfloat16, ops.GLU_SILU, n_tiles=t["n_tiles"], tile_rows=128)
+        act = ops.glu(gu, torch.bfloat16, self.act_kind, n_tiles=t["n_tiles"], tile_rows=128)
         y = torch.empty((rows, W), dtype=torch.float32, device=dev)
         capi.check(core.kb2_linear_bf16_grouped(act.data_ptr(), self.w_down.data_ptr(), y.data_ptr(), rows, W, F, 1, t["tile_expert"].data_ptr(),
                                                 t["n_tiles"].data_ptr(), E, di, s))
         return y, t["pos"]
 
     def route(self, h: torch.Tensor):
-        return ops.route(lin(h, self.w_router, torch.float32, min_n=16), self.correction, self.top, self.groups, self.keep, self.score, self.renorm,
-                         self.out_scale)
+        """(ids, weights, router product [T, >= E + identity] whose column sg_col is the shared expert's gate input)."""
+        z = lin(h, self.w_router, torch.float32, min_n=16)
+        return ops.route(z, self.correction, self.top, self.groups, self.keep, self.score, self.renorm, self.out_scale, self.group_score,
+                         experts=self.E + self.ident) + (z,)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         lib, T, W, E, top = ops.load(), h.shape[0], h.shape[1], self.E, self.top
         dev, s = h.device, torch.cuda.current_stream(h.device).cuda_stream
-        ids, wts = self.route(h)
+        ids, wts, z = self.route(h)
         dt, dtc = self.dtype, ops.dt_code(self.dtype)
         slots = T * top
         y = pos = None
@@ -422,7 +555,7 @@ class RoutedExperts:
             gu = torch.empty((slots, F2), dtype=dt, device=dev)
             ops.check(lib.kb2_seq_moe_gemv(h.data_ptr(), ops.dt_code(h.dtype), h.stride(0), top, ids.data_ptr(), E, self.w_gu.data_ptr(), dtc, W,
                                            F2 * W, gu.data_ptr(), dtc, F2, slots, F2, W, s))
-            act = ops.glu(gu, dt, ops.GLU_SILU)
+            act = ops.glu(gu, dt, self.act_kind)
             y = torch.empty((slots, W), dtype=torch.float32, device=dev)
             ops.check(lib.kb2_seq_moe_gemv(act.data_ptr(), dtc, self.F, 1, ids.data_ptr(), E, self.w_down.data_ptr(), dtc, self.F, W * self.F,
                                            y.data_ptr(), 0, W, slots, W, self.F, s))
@@ -435,14 +568,15 @@ class RoutedExperts:
             gu = torch.empty((max_rows, F2), dtype=dt, device=dev)
             ops.check(lib.kb2_seq_moe_gemm(h.data_ptr(), ops.dt_code(h.dtype), h.stride(0), slot_row.data_ptr(), top, self.w_gu.data_ptr(), dtc, W,
                                            F2 * W, gu.data_ptr(), dtc, F2, F2, W, tile_expert.data_ptr(), n_tiles.data_ptr(), max_tiles, tile, s))
-            act = ops.glu(gu, dt, ops.GLU_SILU, n_tiles=n_tiles, tile_rows=tile)
+            act = ops.glu(gu, dt, self.act_kind, n_tiles=n_tiles, tile_rows=tile)
             y = torch.empty((max_rows, W), dtype=torch.float32, device=dev)
             ops.check(lib.kb2_seq_moe_gemm(act.data_ptr(), dtc, self.F, None, 1, self.w_down.data_ptr(), dtc, self.F, W * self.F, y.data_ptr(), 0,
                                            W, W, self.F, tile_expert.data_ptr(), n_tiles.data_ptr(), max_tiles, tile, s))
         shared = self.shared.forward(h) if self.shared is not None else None
         out = torch.empty((T, W), dtype=torch.float32, device=dev)
+        sg = z[:, self.sg_col:] if (self.sg_col >= 0 and shared is not None) else None
         ops.check(lib.kb2_seq_moe_combine(ops._ptr(y), ops._ptr(pos), ids.data_ptr(), wts.data_ptr(), T, top, E, self.ident, h.data_ptr(),
-                                          ops.dt_code(h.dtype), ops._ptr(shared), out.data_ptr(), W, s))
+                                          ops.dt_code(h.dtype), ops._ptr(shared), out.data_ptr(), W, ops._ptr(sg), z.stride(0), s))
         return out
 
 

@@ -31,6 +31,13 @@ def _megolorn(model_dir, dtype=torch.bfloat16, device=0, **kw):
     return MegolornModel.from_pretrained(model_dir, dtype=dtype, device=device, **kw)
 
 
+def _gurozen(model_dir, dtype=torch.bfloat16, device=0, **kw):
+    from .build import build_seq
+    build_seq()
+    from .gurozen import GurozenModel
+    return GurozenModel.from_pretrained(model_dir, dtype=dtype, device=device, **kw)
+
+
 def _hf_moe(model_dir, dtype=torch.bfloat16, device=0, **kw):
     if dtype != torch.bfloat16:
         raise ValueError("the MoE prefill models run in bfloat16 only")
@@ -42,6 +49,7 @@ def _hf_moe(model_dir, dtype=torch.bfloat16, device=0, **kw):
 
 register("Vofelix", _vofelix)
 register("Megolorn", _megolorn)
+register("Gurozen", _gurozen)
 for _name in _HF_MOE:
     register(_name, _hf_moe)
 

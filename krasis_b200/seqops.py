@@ -25,17 +25,20 @@ SIGNATURES = {
     "kb2_seq_latent_window_attn": (_I, [_P, _P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _F, _I, _P, _P, _I, _I, _P, _P, _P]),
     "kb2_seq_conv_silu": (_I, [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
     "kb2_seq_delta_rule": (_I, [_P, _I, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P, _P, _P, _I, _P]),
+    "kb2_seq_conv": (_I, [_P, _L, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _P, _P, _P]),
+    "kb2_seq_residual_scale_rms": (_I, [_P, _P, _F, _P, _F, _P, _I, _I, _I, _F, _P]),
+    "kb2_seq_delta_rule_ch": (_I, [_P, _I, _P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P, _P, _P, _I, _P]),
     "kb2_seq_residual_add_norm": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
-    "kb2_seq_head_kv_prep": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _P]),
-    "kb2_seq_paged_attn": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _F, _I, _I, _P, _I, _P, _P, _P, _I, _P]),
+    "kb2_seq_head_kv_prep": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _P]),
+    "kb2_seq_paged_attn": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _F, _I, _I, _P, _I, _P, _P, _P, _I, _F, _P]),
     "kb2_seq_attn_finish": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _F, _F, _P, _L, _P, _I, _P, _P, _I, _P]),
     "kb2_seq_glu": (_I, [_P, _I, _L, _P, _I, _L, _I, _I, _F, _F, _P, _I, _P]),
-    "kb2_seq_route": (_I, [_P, _L, _I, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P, _P]),
+    "kb2_seq_route": (_I, [_P, _L, _I, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P]),
     "kb2_seq_moe_tile_rows": (_I, []),
     "kb2_seq_moe_bin": (_I, [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _L, _P, _P]),
     "kb2_seq_moe_gemm": (_I, [_P, _I, _L, _P, _I, _P, _I, _L, _L, _P, _I, _L, _I, _I, _P, _P, _I, _I, _P]),
     "kb2_seq_moe_gemv": (_I, [_P, _I, _L, _I, _P, _I, _P, _I, _L, _L, _P, _I, _L, _I, _I, _I, _P]),
-    "kb2_seq_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _P, _P, _I, _P]),
+    "kb2_seq_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _P, _P, _I, _P, _L, _P]),
 }
 
 _lib = None
@@ -236,26 +239,56 @@ def residual_add_norm(x, y=None, y2=None, out_norm=None, out_dtype=torch.float32
     return h
 
 
-GLU_GELU_TANH, GLU_SILU, GLU_CLAMPED_SWISH = 0, 1, 2
+GLU_GELU_TANH, GLU_SILU, GLU_CLAMPED_SWISH, ACT_RELU2 = 0, 1, 2, 3
 
 
 def glu(gate_up: torch.Tensor, out_dtype, kind: int, limit: float = 0.0, alpha: float = 1.0, n_tiles=None, tile_rows: int = 0) -> torch.Tensor:
-    """[rows, 2F] = [gate | up] -> [rows, F]; see kb2_seq_glu for the kinds."""
+    """[rows, 2F] = [gate | up] -> [rows, F]; ACT_RELU2: [rows, F] -> relu(.)^2 of it, no up half.  See kb2_seq_glu for the kinds."""
     rows, F2 = gate_up.shape
-    out = torch.empty((rows, F2 // 2), dtype=out_dtype, device=gate_up.device)
-    check(load().kb2_seq_glu(gate_up.data_ptr(), dt_code(gate_up.dtype), gate_up.stride(0), out.data_ptr(), dt_code(out_dtype), rows, F2 // 2,
+    F = F2 if kind == ACT_RELU2 else F2 // 2
+    out = torch.empty((rows, F), dtype=out_dtype, device=gate_up.device)
+    check(load().kb2_seq_glu(gate_up.data_ptr(), dt_code(gate_up.dtype), gate_up.stride(0), out.data_ptr(), dt_code(out_dtype), rows, F,
                              int(kind), float(limit), float(alpha), _ptr(n_tiles), int(tile_rows), _s(gate_up)))
     return out
 
 
+def residual_scale_rms(x, y=None, y_mult: float = 1.0, norm=None, w_shift: float = 0.0, out_dtype=torch.float32, eps=1e-5, in_place=False):
+    """x (fp32, in place) += y_mult * y; returns x / rms(x) * (w_shift + norm) in out_dtype (None without `norm`).
+    in_place: the normed row replaces x itself (fp32, no addend)."""
+    T, W = x.shape
+    if y is not None and (y.dtype != torch.float32 or not y.is_contiguous() or y.shape != x.shape):
+        raise ValueError("residual_scale_rms: the addend must be contiguous fp32 of x's shape")
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise ValueError("residual_scale_rms: x must be contiguous fp32")
+    h = None
+    if norm is not None:
+        h = x if in_place else torch.empty((T, W), dtype=out_dtype, device=x.device)
+    check(load().kb2_seq_residual_scale_rms(x.data_ptr(), _ptr(y), float(y_mult), _ptr(norm), float(w_shift), _ptr(h),
+                                            dt_code(h.dtype) if h is not None else 0, T, W, float(eps), _s(x)))
+    return h
+
+
+def conv(proj: torch.Tensor, C: int, taps: torch.Tensor, bias, act: bool, tail: torch.Tensor, tb: "StepTables") -> torch.Tensor:
+    """Short causal convolution over time on the first C columns of proj [T, >= C] fp32 (+ bias), with the carried tail
+    [slots, C, taps - 1] read and advanced; silu on the result if act."""
+    T, K = proj.shape[0], taps.shape[1]
+    out = torch.empty((T, C), dtype=torch.float32, device=proj.device)
+    check(load().kb2_seq_conv(proj.data_ptr(), proj.stride(0), T, tb.S, C, K, taps.data_ptr(), _ptr(bias), int(bool(act)), tail.data_ptr(),
+                              tb.seq_of.data_ptr(), tb.cu.data_ptr(), tb.slots.data_ptr(), out.data_ptr(), _s(proj)))
+    return out
+
+
 def route(z: torch.Tensor, correction, top: int, groups: int = 1, keep: int = 1, score: str = "softmax", renorm: bool = False,
-          out_scale: float = 1.0):
-    """Router logits z [T, E] fp32 -> (ids [T, top] int32, weights [T, top] fp32)."""
+          out_scale: float = 1.0, group_score: str = "max", experts: int = None):
+    """Router logits z [T, >= E] fp32 -> (ids [T, top] int32, weights [T, top] fp32).  experts: E when z carries further columns.
+    group_score: "max" (a group's largest choice) or "top2" (the sum of its two largest)."""
     if z.dtype != torch.float32 or z.stride(1) != 1:
         raise ValueError("route: logits must be fp32 rows")
     T, E = z.shape
+    E = E if experts is None else int(experts)
     ids = torch.empty((T, top), dtype=torch.int32, device=z.device)
     w = torch.empty((T, top), dtype=torch.float32, device=z.device)
     check(load().kb2_seq_route(z.data_ptr(), z.stride(0), T, E, _ptr(correction), {"softmax": 0, "sigmoid": 1}[score], int(groups), int(keep),
-                               int(top), int(renorm), float(out_scale), ids.data_ptr(), w.data_ptr(), _s(z)))
+                               int(top), int(renorm), float(out_scale), ids.data_ptr(), w.data_ptr(), {"max": 0, "top2": 1}[group_score],
+                               _s(z)))
     return ids, w
