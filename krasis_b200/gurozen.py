@@ -118,7 +118,7 @@ def random_weights(cfg: GurozenConfig, seed: int = 0) -> dict:
                 w[p + f"mix.{nm}.conv"] = r(rows, K, sd=0.5)
             rk = max(1, min(W, 16))
             w.update({p + "mix.b": r(H, W, sd=W ** -0.5), p + "mix.a1": r(rk, W, sd=W ** -0.5), p + "mix.a2": r(H * d, rk, sd=rk ** -0.5),
-                      p + "mix.g1": r(rk, W, sd=W ** -0.5), p + "mix.g2": r(H * dv, rk, sd=rk ** -0.5), p + "mix.A_log": r(H, sd=0.5) - 2.0,
+                      p + "mix.g1": r(rk, W, sd=W ** -0.5), p + "mix.g2": r(H * dv, rk, sd=rk ** -0.5), p + "mix.A_log": (r(H, sd=0.5) - 2.0).to(torch.bfloat16).float(),
                       p + "mix.dt_bias": r(H * d, sd=0.5), p + "mix.norm": (1.0 + 0.1 * torch.randn(dv, generator=g)).to(torch.bfloat16).float()})
         w[p + "mix.o"] = r(W, H * dv, sd=(H * dv) ** -0.5)
         mlp = L.get("mlp")
