@@ -486,10 +486,11 @@ def main():
     ap.add_argument("--cpu-format", default="int4", choices=["int4", "gguf"],
                     help="CPU arm: int4 = moe_forward_unified on INT4 g128 (default); gguf = moe_forward_gguf on native Q4_K/Q8_0 blocks "
                          "(BASELINE configs[0]: --config v2lite --impl reference --cpu-format gguf --tokens 2048)")
-    ap.add_argument("--arch", default="moe", choices=["moe", "vofelix", "megolorn"],
+    ap.add_argument("--arch", default="moe", choices=["moe", "vofelix", "megolorn", "gurozen"],
                     help="moe (default): the BASELINE workload above; vofelix: prefill / decode throughput of the ragged-batch model at "
                          "real layer sizes beside the Gated-DeltaNet and MLA blocks at equal size (1 GPU); megolorn: the same for the "
-                         "differential-attention / routed-expert model beside Vofelix and the GQA block at equal size")
+                         "differential-attention / routed-expert model beside Vofelix and the GQA block at equal size; gurozen: the same for "
+                         "the capped-attention / channel-decay delta rule / squared-relu expert model beside the Megolorn and Vofelix blocks")
     args = ap.parse_args()
     if args.arch == "vofelix":
         from krasis_b200.bench_seq import run as run_seq
@@ -498,6 +499,10 @@ def main():
     if args.arch == "megolorn":
         from krasis_b200.bench_seq import run_megolorn
         run_megolorn(args, peaks())
+        return
+    if args.arch == "gurozen":
+        from krasis_b200.bench_seq import run_gurozen
+        run_gurozen(args, peaks())
         return
     args.tokens = args.tokens or DEFAULT_TOKENS[args.config]
     if args.impl == "reference":

@@ -369,6 +369,10 @@ KB2_API int kb2_fmha_latent(const void* q_dev, const void* kv_up_dev, const void
 KB2_API int kb2_fmha_maps(const void* q_dev, const void* k_dev, const void* v_dev, float* out_dev, int32_t M, int32_t q_start,
                           int32_t kv_len, int32_t num_q, int32_t num_kv_heads, int32_t maps, int32_t v_dim, float sm_scale, int32_t window,
                           int32_t device, void* stream);
+/* The same with tanh soft-capped scores: a scaled score s becomes softcap * tanh(s / softcap) before the softmax (softcap 0: none). */
+KB2_API int kb2_fmha_maps_softcap(const void* q_dev, const void* k_dev, const void* v_dev, float* out_dev, int32_t M, int32_t q_start,
+                                  int32_t kv_len, int32_t num_q, int32_t num_kv_heads, int32_t maps, int32_t v_dim, float sm_scale,
+                                  float softcap, int32_t window, int32_t device, void* stream);
 
 /* GEMM -> reduce-scatter fused (head-parallel attention under token sharding): after kb2_{gdn,gqa,mla}_set_output_scatter the
  * block's out_proj GEMM stores every output row straight into the receive buffer of the rank that owns the token

@@ -1,4 +1,4 @@
-"""Throughput of the ragged-batch models (Vofelix, Megolorn) at layer sizes of real models, beside the framework's closest existing blocks at
+"""Throughput of the ragged-batch models (Vofelix, Megolorn, Gurozen) at layer sizes of real models, beside the framework's closest existing blocks at
 equal size: prefill tokens/s (one prompt, whole and in portions), decode tokens/s (several live requests, one token each per step),
 and per-mixer times — the gated delta mixer against the Gated-DeltaNet block, windowed latent attention against the MLA block.
 Random weights; device timing with CUDA events after warm-up; the weights of a step exceed the L2 cache."""
@@ -254,6 +254,130 @@ def run_megolorn(args, peaks):
             gqa.forward(h, pos, kv, st, 0, num_new_tokens=tokens)
             st.free()
         blk["gqa_block_16x256_full_causal_ms"] = round(_time(gqa_step, 2, 5), 3)
+    except Exception as exc:       # noqa: BLE001 — the comparison is optional; the new design's numbers stand without it
+        blk["comparison_unavailable"] = f"{type(exc).__name__}: {exc}"
+    out["blocks_at_equal_size"] = blk
+    out["peaks"] = peaks
+    print(json.dumps(out))
+
+
+# ------------------------------------------------------------------------------------------------ Gurozen
+def gurozen_config(width=2048, vocab=32768, experts=64, top=6, expert_ff=1024):
+    """Attention 16 heads x 128 over 2 key/value heads (the score product of Qwen3-Next's GQA block at half the value width), the
+    channel-decay delta rule at Qwen3-Next's linear-attention geometry (32 / 16 heads x 128), 64 squared-relu experts in 8 groups
+    (4 kept, top 6) with a gated shared expert; layers 1 and 2 run twice."""
+    att = {"heads": 16, "kv_heads": 2, "dim": 128, "vdim": 128, "conv": 3, "scale": 128 ** -0.5, "softcap": 30.0,
+           "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    delta = {"heads": 32, "kv_heads": 16, "dim": 128, "vdim": 128, "conv": 4}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": 2 * expert_ff},
+           "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": 8, "keep": 4}}}
+    dense = {"kind": "dense", "ff": 4 * width}
+    layers = [{"type": "attention", "mixer": att, "mlp": dense}, {"type": "channel_delta", "mixer": delta, "mlp": moe},
+              {"type": "attention", "mixer": att, "mlp": moe}, {"type": "channel_delta", "mixer": delta, "mlp": dense}]
+    return {"architecture": "Gurozen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5, "logit_scale": 0.5,
+            "loop": {"start": 1, "stop": 3, "times": 2}, "layers": layers}
+
+
+def run_gurozen(args, peaks):
+    from . import seqops as ops
+    from .build import build, build_seq
+    build_seq()
+    build()                                          # the tcgen05 GEMM and attention core serve long bfloat16 steps
+    from .gurozen import GurozenConfig, GurozenModel
+    from .scheduler import Scheduler
+    dev = torch.device("cuda", 0)
+    tokens = args.tokens or 4096
+    raw = gurozen_config()
+    cfg = GurozenConfig.from_dict(raw)
+    model = GurozenModel.random(cfg, seed=0, dtype=torch.bfloat16, device=0)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (tokens,), generator=g).tolist()
+    out = {"metric": "gurozen_prefill_tokens_per_s", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+           "higher_is_better": True, "dtype": "bf16", "data": "synthetic (random weights and token ids)", "vs_baseline": None,
+           "config": {"model": "gurozen width 2048: 4 layers (attention 16 heads x 128 / 2 kv heads, conv 3, cap 30; channel-decay delta rule "
+                               "32 / 16 heads x 128, conv 4), layers 1..2 run twice = 6 layer runs; dense ff 8192 / 64 squared-relu experts in 8 "
+                               "groups, top 6, expert ff 1024, gated shared ff 2048", "prompt_tokens": tokens,
+                      "l2": "weights of one step (about 1.3 GB) exceed L2"}}
+    launches0 = ops.total_launches()
+
+    def prefill(portion):
+        s = Scheduler(model, max_tokens=tokens + 64, max_requests=4)
+        at = 0
+        while at < tokens:
+            n = min(portion, tokens - at)
+            lg = s.step([("p", prompt[at:at + n], [n - 1] if at + n == tokens else [])])
+            at += n
+        s.finish("p")
+        return lg
+    ms = _time(lambda: prefill(tokens), args.warmup, args.steps)
+    out.update(value=round(tokens / ms * 1e3, 1), ms_per_step=round(ms, 3))
+    ms_p = _time(lambda: prefill(512), 1, max(1, args.steps // 2))
+    out["prefill_portions_512"] = {"tokens_per_s": round(tokens / ms_p * 1e3, 1), "ms": round(ms_p, 3)}
+
+    ctx = 2048
+    s = Scheduler(model, max_tokens=4 * (ctx + 256), max_requests=4, cuda_graphs=not getattr(args, 'no_graph', False))
+    for r in range(4):
+        s.step([(r, prompt[:ctx], [])])
+    nxt = [[1], [2], [3], [4]]
+    ms_d = _time(lambda: s.step([(r, nxt[r], [0]) for r in range(4)]), args.warmup, 16)
+    out["decode"] = {"live_requests": 4, "context": ctx, "tokens_per_s": round(4 / ms_d * 1e3, 1), "ms_per_step": round(ms_d, 3),
+                     "cuda_graph": bool(s.cuda_graphs and any(v not in (None, False) for v in s._graphs.values()))}
+    out["gpu_launches"] = ops.total_launches() - launches0
+
+    s = Scheduler(model, max_tokens=tokens + 256, max_requests=4)
+    s.generate([prompt], max_new_tokens=8, step_tokens=tokens)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    h2d0, steps0 = s.h2d_bytes, s.steps_run
+    t0.record()
+    s.generate([prompt], max_new_tokens=8, step_tokens=tokens)
+    t1.record()
+    torch.cuda.synchronize()
+    out["e2e"] = {"value": round((tokens + 8) / t0.elapsed_time(t1) * 1e3, 1), "unit": "tokens/s (prompt + 8 generated, Scheduler.generate)",
+                  "h2d_bytes_per_step": (s.h2d_bytes - h2d0) // max(s.steps_run - steps0, 1), "d2h_bytes_per_step": 8}
+
+    # ---- per-block times, prefill and decode, beside the closest blocks of the other designs at equal size
+    blk = {}
+    W = cfg.width
+    h = (torch.randn(tokens, W, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+    pages = list(range((tokens + 63) // 64))
+    tb = ops.StepTables([(prompt, 0, 0, pages)], dev)
+    model.make_caches(tokens + 64, 4)
+    att, dl = model.layers[0]["mixer"], model.layers[1]["mixer"]
+    kc, vc = model.kv_cache.get_layer_caches(0)
+    blk["attention_block_ms"] = round(_time(lambda: att.forward(h, tb, kc, vc, 64, tail=model._run_state[0]), 2, 5), 3)
+    tail, state = model._run_state[1]
+    blk["channel_delta_mixer_ms"] = round(_time(lambda: dl.forward(h, tb, tail, state), 2, 5), 3)
+    blk["dense_ff_8192_ms"] = round(_time(lambda: model.layers[0]["mlp"].forward(h), 2, 5), 3)
+    moe = model.layers[1]["mlp"]
+    blk["routed_experts_block_ms"] = round(_time(lambda: moe.forward(h), 2, 5), 3)
+    h4 = h[:4].contiguous()
+    tb4 = ops.StepTables([([1], ctx, r, list(range(r * 40, r * 40 + 33))) for r in range(4)], dev)
+    blk["decode_4_tokens_attention_ms"] = round(_time(lambda: att.forward(h4, tb4, kc, vc, 64, tail=model._run_state[0]), 3, 20), 4)
+    blk["decode_4_tokens_channel_delta_ms"] = round(_time(lambda: dl.forward(h4, tb4, tail, state), 3, 20), 4)
+    blk["decode_4_tokens_routed_experts_ms"] = round(_time(lambda: moe.forward(h4), 3, 20), 4)
+    try:                                             # the closest blocks: Megolorn's attention and experts, Vofelix's delta mixer
+        from .attention import HeadKVCache, RecurrentStatePool
+        from .megolorn import MegolornConfig, MegolornModel
+        from .vofelix import VofelixConfig, VofelixModel
+        mraw = megolorn_config(experts=64, identity=0)
+        mraw["layers"] = mraw["layers"][:2]
+        mraw["layers"][0]["mixer"]["vdim"] = mraw["layers"][1]["mixer"]["vdim"] = 128
+        mm = MegolornModel.random(MegolornConfig.from_dict(mraw), seed=0, dtype=torch.bfloat16, device=0)
+        matt, mmoe = mm.layers[0]["mixer"], mm.layers[1]["mlp"]
+        mkv = HeadKVCache([matt.cache_dims()], dev, max_pages=len(pages) + 1, dtype=torch.bfloat16, page_size=64)
+        mk, mv = mkv.get_layer_caches(0)
+        blk["megolorn_attention_block_2_maps_ms"] = round(_time(lambda: matt.forward(h, tb, mk, mv, 64), 2, 5), 3)
+        blk["megolorn_routed_experts_block_ms"] = round(_time(lambda: mmoe.forward(h), 2, 5), 3)
+        blk["megolorn_decode_4_tokens_routed_experts_ms"] = round(_time(lambda: mmoe.forward(h4), 3, 20), 4)
+        vraw, _, _ = bench_config()
+        vraw["layers"] = vraw["layers"][:1]
+        vraw["loop"] = {"start": 0, "stop": 0, "times": 1}
+        vm = VofelixModel.random(VofelixConfig.from_dict(vraw), seed=0, dtype=torch.bfloat16, device=0)
+        vd = vm.layers[0]["mixer"]
+        vt, vs = vd.register_state(RecurrentStatePool(4, dev))
+        blk["vofelix_delta_mixer_ms"] = round(_time(lambda: vd.forward(h, tb, vt, vs), 2, 5), 3)
+        blk["vofelix_decode_4_tokens_delta_ms"] = round(_time(lambda: vd.forward(h4, tb4, vt, vs), 3, 20), 4)
     except Exception as exc:       # noqa: BLE001 — the comparison is optional; the new design's numbers stand without it
         blk["comparison_unavailable"] = f"{type(exc).__name__}: {exc}"
     out["blocks_at_equal_size"] = blk

@@ -183,7 +183,9 @@ __global__ void __launch_bounds__(kFThreads, 1)
                     const float* __restrict__ sinks = nullptr,   // per head: exp(sink) joins the softmax denominator (no value)
                     int maps = 1,                                // query heads come in groups of `maps` attention maps: map m of a head reads
                                                                  // key head kvh * maps + m, every map reads value head kvh
-                    float* __restrict__ out_f32 = nullptr) {     // if given, the output rows are written here in fp32 (no gate), not to `out`
+                    float* __restrict__ out_f32 = nullptr,       // if given, the output rows are written here in fp32 (no gate), not to `out`
+                    float cap_in = 0.f, float cap_out = 0.f) {   // soft cap: a raw score s becomes cap_out * tanh(s * cap_in) with
+                                                                 // cap_in = sm_scale / cap, cap_out = cap / sm_scale (0: no cap)
   using L = FmhaSmem<DQ, DV>;
   constexpr int D = DQ;
   constexpr int NC = DQ / 64;                      // 64-wide d chunks of q/k
@@ -383,6 +385,11 @@ __global__ void __launch_bounds__(kFThreads, 1)
       }
       tc_fence_before_sync();
       mbar_arrive(s_cons);                         // S may be overwritten by the next QK^T
+      if (cap_in != 0.f) {                         // tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1): exact limits at +-inf, two MUFU ops per score
+        const float c2 = cap_in * 2.8853900817779268f;
+#pragma unroll
+        for (int jj = 0; jj < KH; ++jj) s[jj] = cap_out * (1.f - __fdividef(2.f, ex2_approx(s[jj] * c2) + 1.f));
+      }
       const int key0 = (it + tile0) * kFK + hf * KH;
       // causal / length / window mask only where a key of this half-tile can be invisible to a row of this warp (warp-uniform)
       if (key0 + KH - 1 > q_start + q0 + q * 32 || key0 + KH > kv_len || key0 + window <= q_start + q0 + q * 32 + 31) {
@@ -746,8 +753,11 @@ cudaError_t launch_fmha_latent(const void* q, const void* kv_up, const void* kpe
 // Attention core on dense BF16 rows for heads that carry several attention maps: q [M][nq * 128] with nq = heads * maps query
 // vectors (head by head, map by map), k [kv_len][nkv * maps * 128], v [kv_len][nkv * dv], dv 128 or 256; out_f32 [M][nq * dv] fp32.
 // Query i stands at position q_start + i of the kv rows and sees the keys with 0 <= position - key < window.
+// softcap > 0: a scaled score s becomes softcap * tanh(s / softcap).
 cudaError_t launch_fmha_maps(const void* q, const void* k, const void* v, float* out_f32, int M, int q_start, int kv_len, int nq, int nkv,
-                             int maps, int dv, float sm_scale, int window, cudaStream_t s) {
+                             int maps, int dv, float sm_scale, int window, cudaStream_t s, float softcap) {
+  if (!(softcap >= 0.f) || !(sm_scale > 0.f)) return cudaErrorInvalidValue;
+  const float cap_in = softcap > 0.f ? sm_scale / softcap : 0.f, cap_out = softcap > 0.f ? softcap / sm_scale : 0.f;
   if (M <= 0 || nq <= 0 || nkv <= 0 || maps <= 0 || nq % maps || (nq / maps) % nkv || q_start < 0 || kv_len != q_start + M || window <= 0 ||
       (dv != 128 && dv != 256))
     return cudaErrorInvalidValue;
@@ -772,10 +782,10 @@ cudaError_t launch_fmha_maps(const void* q, const void* k, const void* v, float*
   const float sl2 = sm_scale * 1.4426950408889634f;
   if (dv == 256)
     gqa_fmha_kernel<128, 256, false><<<grid, kFThreads, FmhaSmem<128, 256>::kTotal, s>>>(tq, tk, tk, tv, g, nullptr, nullptr, M, q_start, kv_len,
-                                                                                          sl2, 0, 0, window, nullptr, maps, out_f32);
+                                                                                          sl2, 0, 0, window, nullptr, maps, out_f32, cap_in, cap_out);
   else
     gqa_fmha_kernel<128, 128, false><<<grid, kFThreads, FmhaSmem<128, 128>::kTotal, s>>>(tq, tk, tk, tv, g, nullptr, nullptr, M, q_start, kv_len,
-                                                                                          sl2, 0, 0, window, nullptr, maps, out_f32);
+                                                                                          sl2, 0, 0, window, nullptr, maps, out_f32, cap_in, cap_out);
   return cudaGetLastError();
 }
 

@@ -402,9 +402,9 @@ class MultiMapAttention:
             end = min(start + n, cstart + chunk) if chunk else start + n
             lo = max(cstart, first)
             m = end - pos
-            capi.check(core.kb2_fmha_maps(q[pos - start:].data_ptr(), k_rows[lo - first:].data_ptr(), v_rows[lo - first:].data_ptr(),
-                                          a[row0 + pos - start:].data_ptr(), m, pos - lo, end - lo, H * M, G, M, dv, self.scale,
-                                          min(self.window, 1 << 30), proj.device.index or 0, stream))
+            capi.check(core.kb2_fmha_maps_softcap(q[pos - start:].data_ptr(), k_rows[lo - first:].data_ptr(), v_rows[lo - first:].data_ptr(),
+                                                  a[row0 + pos - start:].data_ptr(), m, pos - lo, end - lo, H * M, G, M, dv, self.scale,
+                                                  self.softcap, min(self.window, 1 << 30), proj.device.index or 0, stream))
             pos = end
 
     def forward(self, h: torch.Tensor, tb: ops.StepTables, kc: torch.Tensor, vc: torch.Tensor, page_size: int, tail=None) -> torch.Tensor:
@@ -424,7 +424,7 @@ class MultiMapAttention:
         reach = min(self.window, self.chunk) if self.chunk else self.window
         max_keys = max(min(reach, start + n) for _, n, start, _ in tb.layout)
         nsplit = max(1, min(296 // max(T * G, 1), (max_keys + 31) // 32, 64))
-        core = _core_lib() if (self.tc_shape and self.softcap == 0.0) else False
+        core = _core_lib() if self.tc_shape else False
         fast = [i for i, (_, n, _, _) in enumerate(tb.layout) if n >= self.tc_min_portion] if core else []
         if fast:
             nsplit = 1

@@ -474,6 +474,40 @@ def test_bfloat16_serving_close_to_oracle(seq):
     most(b, a.astype(np.float64), 6e-2, "bf16: portions against whole")
 
 
+def test_tensor_core_prefill_of_capped_attention_and_experts(seq):
+    """bfloat16 with 128 query / key dims and 128 or 256 value dims: portions of 128 tokens or more run the tcgen05 attention core (the cap
+    applied to its scores), long steps run the routed experts as grouped tcgen05 GEMMs.  Against the oracle and against the plain
+    kernels on the same bf16 cache, with scores large enough for the cap to bite."""
+    from krasis_b200.build import build as build_core
+    build_core()
+    for vdim, heads, kv_heads, cap in ((128, 2, 1, 4.0), (256, 4, 2, 2.5), (128, 2, 2, 0.0)):
+        layers = [A(attn(heads=heads, kv_heads=kv_heads, dim=128, vdim=vdim, rot_dims=64, conv=3, scale=0.6, softcap=cap), dense(ff=64)),
+                  D(delta(heads=2, kv_heads=1, dim=64, vdim=64), moe(experts=8, top=2, groups=4, keep=2, ff=64, shared=64))]
+        raw = model_cfg(layers, width=64, loop=(0, 1, 2))
+        model, w = build(raw, dtype=torch.bfloat16, seed=31)
+        mixer, rx = model.layers[0]["mixer"], model.layers[1]["mlp"]
+        assert mixer.tc_shape
+        tk = toks(700, raw["vocab"], 16)
+        want = O.forward(raw, w, tk)
+        if cap:                                     # the cap must move the logits by far more than the tolerances below
+            loose = json.loads(json.dumps(raw))
+            loose["layers"][0]["mixer"]["softcap"] = 0.0
+            assert np.abs(O.forward(loose, w, tk) - want).max() > 0.15 * np.abs(want).max()
+
+        def most(got, ref, rel, what):              # a router choice may fall the other way in bfloat16: four positions out of five
+            err = np.abs(got.astype(np.float64) - ref).max(-1) / np.abs(ref).max()
+            assert np.quantile(err, 0.8) <= rel, f"{what}: {np.quantile(err, 0.8):.3e}"
+        fast_whole = run_portions(model, tk, [700], s=sched(model, 1024))
+        fast_parts = run_portions(model, tk, [130, 257, 128, 150], s=sched(model, 1024))          # then 35 single tokens through the plain kernels
+        mixer.tc_min_portion, rx.tc_min_rows_per_expert = 1 << 30, 1 << 30
+        plain = run_portions(model, tk, [700], s=sched(model, 1024))
+        mixer.tc_min_portion, rx.tc_min_rows_per_expert = 128, 16
+        most(plain, want, 5e-2, f"cap {cap}: plain kernels against the oracle")
+        most(fast_whole, want, 5e-2, f"cap {cap}: tensor-core prefill against the oracle")
+        most(fast_whole, plain.astype(np.float64), 3e-2, f"cap {cap}: tensor-core prefill against the plain kernels")
+        most(fast_parts, plain.astype(np.float64), 3e-2, f"cap {cap}: tensor-core portions against the plain kernels")
+
+
 def test_greedy_generation_through_the_entry_point(seq):
     """Scheduler.generate (admission, portions under a token budget, decode beside prefill, slot and page reuse) against greedy
     decoding with the oracle.  Steps whose two best logits are closer than the comparison tolerance end the comparison of a prompt."""
