@@ -68,11 +68,12 @@ __device__ __forceinline__ float silu(float z) { return z / (1.f + expf(-z)); }
 // Per-token decay exp(-exp(A_log) * softplus(a + dt_bias)).  A recurrent state multiplies by it at every token, so a rounding bias of
 // the fp32 exp / log1p chain (a fraction of an ulp, but of one sign) would grow linearly with the distance to a far token; evaluated in
 // fp64 and rounded once, the fp32 decay carries only its own unbiased half ulp.
-__device__ __forceinline__ float decay_of(float a_log, float a, float dt_bias) {
+__device__ __forceinline__ float decay_from_rate(double rate, float a, float dt_bias) {      // rate = exp(A_log) in fp64
   const double z = (double)a + (double)dt_bias;
   const double sp = z > 40.0 ? z : log1p(exp(z));
-  return (float)exp(-exp((double)a_log) * sp);
+  return (float)exp(-rate * sp);
 }
+__device__ __forceinline__ float decay_of(float a_log, float a, float dt_bias) { return decay_from_rate(exp((double)a_log), a, dt_bias); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -261,22 +261,31 @@ __global__ void __launch_bounds__(256) attn_finish_kernel(const float* __restric
   for (int m = 0; m < M; ++m) {
     const long long row = w * M + m;
     const float cm = coef ? coef[m] : 1.f;
-    if (nsplit > 1) {
+    if (nsplit > 1) {                        // the pieces' maxima and sums are spread over the lanes; weights travel by shuffle
       float mx = -INFINITY;
-      for (int z = 0; z < nsplit; ++z) mx = fmaxf(mx, part_ml[(row * nsplit + z) * 2]);
+      for (int z = lane; z < nsplit; z += 32) mx = fmaxf(mx, part_ml[(row * nsplit + z) * 2]);
+      mx = warp_max(mx);
       float den = 0.f;
-      for (int z = 0; z < nsplit; ++z) {
+      for (int z = lane; z < nsplit; z += 32) {
         const float mz = part_ml[(row * nsplit + z) * 2];
         if (mz != -INFINITY) den += expf(mz - mx) * part_ml[(row * nsplit + z) * 2 + 1];
       }
-      for (int z = 0; z < nsplit; ++z) {
-        const float mz = part_ml[(row * nsplit + z) * 2];
-        if (mz == -INFINITY) continue;
-        const float wz = expf(mz - mx) / den * cm;
+      den = warp_sum(den);
+      for (int z0 = 0; z0 < nsplit; z0 += 32) {
+        float wl = 0.f;
+        if (z0 + lane < nsplit) {
+          const float mz = part_ml[(row * nsplit + z0 + lane) * 2];
+          if (mz != -INFINITY) wl = expf(mz - mx) / den * cm;
+        }
+        const int nz = min(32, nsplit - z0);
+        for (int k = 0; k < nz; ++k) {
+          const float wz = __shfl_sync(0xffffffffu, wl, k);
+          if (wz == 0.f) continue;            // the same for every lane
 #pragma unroll
-        for (int i = 0; i < kFinAcc; ++i) {
-          const int c = lane + 32 * i;
-          if (c < dv) o[i] = fmaf(wz, part_acc[(row * nsplit + z) * dv + c], o[i]);
+          for (int i = 0; i < kFinAcc; ++i) {
+            const int c = lane + 32 * i;
+            if (c < dv) o[i] = fmaf(wz, part_acc[(row * nsplit + z0 + k) * dv + c], o[i]);
+          }
         }
       }
     } else {

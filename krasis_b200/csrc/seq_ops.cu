@@ -620,6 +620,49 @@ __global__ void conv_silu_kernel(const float* __restrict__ proj, long long ldp, 
   out[idx] = act ? silu(acc) : acc;
 }
 
+// The same for long steps and K <= kConvMaxTaps: a thread owns a channel over kConvRun consecutive rows and keeps the last K inputs in
+// registers, so that every input is read once (plus K - 1 rows of overlap per run) instead of K times.
+constexpr int kConvMaxTaps = 8, kConvRun = 16;
+__global__ void __launch_bounds__(256) conv_run_kernel(const float* __restrict__ proj, long long ldp, int C, int K,
+                                                       const float* __restrict__ taps, const float* __restrict__ tail,
+                                                       const int* __restrict__ seq_of, const int* __restrict__ cu,
+                                                       const int* __restrict__ slots, long long T, float* __restrict__ out,
+                                                       const float* __restrict__ bias, int act) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const long long r0 = (long long)blockIdx.y * kConvRun, r1 = min(T, r0 + kConvRun);
+  float w[kConvMaxTaps], x[kConvMaxTaps] = {};     // x[j]: the input K - 1 - j rows back, x[K - 1] the current one
+#pragma unroll
+  for (int j = 0; j < kConvMaxTaps; ++j) w[j] = j < K ? taps[(long long)c * K + j] : 0.f;
+  const float b = bias != nullptr ? bias[c] : 0.f;
+  int s = -1;
+  for (long long t = r0; t < r1; ++t) {
+    const int st = seq_of[t];
+    if (st != s || t == r0) {                        // first row of this run, or of another sequence: fetch the K - 1 earlier inputs
+      s = st;
+      const int i = (int)(t - cu[s]);
+      const float* tl = tail + ((long long)slots[s] * C + c) * (K - 1);
+#pragma unroll
+      for (int j = 0; j < kConvMaxTaps - 1; ++j)
+        if (j < K - 1) {
+          const int src = i - (K - 1) + j;
+          x[j + 1] = src >= 0 ? proj[(t - i + src) * ldp + c] + b : tl[(K - 1) + src];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kConvMaxTaps - 1; ++j) x[j] = x[j + 1];
+    // after the shift x[0 .. K - 2] hold the K - 1 earlier inputs; the current one goes to x[K - 1]
+    const float cur = proj[t * ldp + c] + b;
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < kConvMaxTaps; ++j) {
+      if (j == K - 1) x[j] = cur;
+      if (j < K) acc = fmaf(w[j], x[j], acc);
+    }
+    out[t * C + c] = act ? silu(acc) : acc;
+  }
+}
+
 // after the convolution: the tail becomes the last K - 1 inputs seen so far (one thread per (sequence, channel), ascending order)
 __global__ void conv_tail_kernel(const float* __restrict__ proj, long long ldp, int C, int K, float* __restrict__ tail,
                                  const int* __restrict__ cu, const int* __restrict__ slots, int S, const float* __restrict__ bias) {
@@ -660,7 +703,8 @@ __global__ void __launch_bounds__(1024) delta_rule_kernel(const float* __restric
   const int t0 = cu[s], n = cu[s + 1] - cu[s];
   float* Sg = state + ((long long)slots[s] * H + h) * dk * dv;
   for (int i = tid; i < dk * dv; i += blockDim.x) S[i] = Sg[i];
-  const float a_log_h = A_log[h], qscale = 1.f / sqrtf((float)dk);
+  const double rate_h = exp((double)A_log[h]);
+  const float qscale = 1.f / sqrtf((float)dk);
   const int q_col = hk * dk, k_col = Hk * dk + hk * dk, v_col = 2 * Hk * dk + h * dv;
   for (int b0 = 0; b0 < n; b0 += kDeltaTile) {
     const int nt = min(kDeltaTile, n - b0);
@@ -681,7 +725,7 @@ __global__ void __launch_bounds__(1024) delta_rule_kernel(const float* __restric
         kn[tt * dk + i] = row[k_col + i] * rk;
       }
       const float* ar = aproj + (long long)(t0 + b0 + tt) * lda + (long long)h * dstr;
-      for (int i = lane; i < dstr; i += 32) dec[tt * dstr + i] = decay_of(a_log_h, ar[i], dt_bias[h * dstr + i]);
+      for (int i = lane; i < dstr; i += 32) dec[tt * dstr + i] = decay_from_rate(rate_h, ar[i], dt_bias[h * dstr + i]);
       if (lane == 0) beta[tt] = 1.f / (1.f + expf(-bproj[(long long)(t0 + b0 + tt) * ldb + h]));
     }
     __syncthreads();
@@ -762,9 +806,13 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(const float* __restrict
     if (!ch) dec[t * H + h] = decay_of(A_log[h], aproj[t * lda + h], dt_bias[h]);
   }
   if (ch)                                    // one decay per key channel of each of this key head's heads: dec [T][H][dk]
-    for (int e = lane; e < rep * dk; e += 32) {
-      const long long c = (long long)hk * rep * dk + e;
-      dec[t * H * dk + c] = decay_of(A_log[c / dk], aproj[t * lda + c], dt_bias[c]);
+    for (int j = 0; j < rep; ++j) {
+      const int h = hk * rep + j;
+      const double rate = exp((double)A_log[h]);
+      for (int i = lane; i < dk; i += 32) {
+        const long long c = (long long)h * dk + i;
+        dec[t * H * dk + c] = decay_from_rate(rate, aproj[t * lda + c], dt_bias[c]);
+      }
     }
 }
 
@@ -1050,8 +1098,12 @@ KB2SEQ_API int kb2_seq_conv(const float* proj, long long ldp, int T, int S, int 
   if (!proj || !taps || !tail || !seq_of || !cu || !slots || !out || T <= 0 || S <= 0 || C <= 0 || K <= 0 || act < 0 || act > 1)
     return failf(KB2SEQ_ERR_VALUE, "conv: bad argument");
   if (T > 65535) return failf(KB2SEQ_ERR_VALUE, "conv: more than 65535 rows in one step");
-  conv_silu_kernel<<<dim3((C + 255) / 256, T), 256, 0, (cudaStream_t)stream>>>(proj, ldp, C, K, taps, tail, seq_of, cu, slots, T, out, bias,
-                                                                               act);
+  if (T >= 4 * kConvRun && K <= kConvMaxTaps)
+    conv_run_kernel<<<dim3((C + 255) / 256, (T + kConvRun - 1) / kConvRun), 256, 0, (cudaStream_t)stream>>>(proj, ldp, C, K, taps, tail, seq_of,
+                                                                                                          cu, slots, T, out, bias, act);
+  else
+    conv_silu_kernel<<<dim3((C + 255) / 256, T), 256, 0, (cudaStream_t)stream>>>(proj, ldp, C, K, taps, tail, seq_of, cu, slots, T, out, bias,
+                                                                                 act);
   SEQ_LAUNCHED();
   if (K > 1) {
     const long long m = (long long)S * C;

@@ -237,10 +237,12 @@ class ChannelDeltaMixer:
         return pool.register(self.C, max(self.K - 1, 1)), pool.register(self.H, self.dk, self.dv)
 
     def _second(self, proj, off, r, w):
+        """Second factor of a low-rank projection on columns [off, off + r) of the fp32 first product.  The generic kernel reads the
+        strided fp32 columns as they are; only a long bfloat16 step with a rank the tensor-core kernel takes is rounded and packed."""
         a = proj[:, off:off + r]
-        if self.dtype == torch.bfloat16:
-            a = a.to(torch.bfloat16)
-        return lin(a.contiguous(), w, torch.float32)
+        if self.dtype == torch.bfloat16 and proj.shape[0] >= 256 and r % 64 == 0 and _core_lib():
+            return lin(a.to(torch.bfloat16).contiguous(), w, torch.float32)
+        return ops.gemm(a, w, torch.float32)
 
     def forward(self, h: torch.Tensor, tb: ops.StepTables, tail: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
         lib, T, H = ops.load(), h.shape[0], self.H
