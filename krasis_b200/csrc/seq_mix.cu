@@ -278,9 +278,10 @@ __global__ void __launch_bounds__(256) attn_finish_kernel(const float* __restric
           if (mz != -INFINITY) wl = expf(mz - mx) / den * cm;
         }
         const int nz = min(32, nsplit - z0);
+        // an empty piece holds zeros and has weight 0, so nothing is skipped and the loads of several pieces are in flight together
+#pragma unroll 8
         for (int k = 0; k < nz; ++k) {
           const float wz = __shfl_sync(0xffffffffu, wl, k);
-          if (wz == 0.f) continue;            // the same for every lane
 #pragma unroll
           for (int i = 0; i < kFinAcc; ++i) {
             const int c = lane + 32 * i;
