@@ -266,15 +266,15 @@ def gurozen_config(width=2048, vocab=32768, experts=64, top=6, expert_ff=1024):
     """Attention 16 heads x 128 over 2 key/value heads (the score product of Qwen3-Next's GQA block at half the value width), the
     channel-decay delta rule at Qwen3-Next's linear-attention geometry (32 / 16 heads x 128), 64 squared-relu experts in 8 groups
     (4 kept, top 6) with a gated shared expert; layers 1 and 2 run twice."""
-    att = {"heads": 16, "kv_heads": 2, "dim": 128, "vdim": 128, "conv": 3, "scale": 128 ** -0.5, "softcap": 30.0,
-           "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    att = {"heads": 16, "kv_heads": 2, "dim": 128, "vdim": 128, "conv": 4, "scale": 128 ** -0.5, "softcap": 50.0,
+           "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 8.0, "original": 8192}}}
     delta = {"heads": 32, "kv_heads": 16, "dim": 128, "vdim": 128, "conv": 4}
     moe = {"kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": 2 * expert_ff},
            "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": 8, "keep": 4}}}
     dense = {"kind": "dense", "ff": 4 * width}
     layers = [{"type": "attention", "mixer": att, "mlp": dense}, {"type": "channel_delta", "mixer": delta, "mlp": moe},
               {"type": "attention", "mixer": att, "mlp": moe}, {"type": "channel_delta", "mixer": delta, "mlp": dense}]
-    return {"architecture": "Gurozen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5, "logit_scale": 0.5,
+    return {"architecture": "Gurozen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.7, "logit_scale": 0.25,
             "loop": {"start": 1, "stop": 3, "times": 2}, "layers": layers}
 
 
@@ -294,7 +294,7 @@ def run_gurozen(args, peaks):
     prompt = torch.randint(0, cfg.vocab, (tokens,), generator=g).tolist()
     out = {"metric": "gurozen_prefill_tokens_per_s", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
            "higher_is_better": True, "dtype": "bf16", "data": "synthetic (random weights and token ids)", "vs_baseline": None,
-           "config": {"model": "gurozen width 2048: 4 layers (attention 16 heads x 128 / 2 kv heads, conv 3, cap 30; channel-decay delta rule "
+           "config": {"model": "gurozen width 2048: 4 layers (attention 16 heads x 128 / 2 kv heads, conv 4, cap 50; channel-decay delta rule "
                                "32 / 16 heads x 128, conv 4), layers 1..2 run twice = 6 layer runs; dense ff 8192 / 64 squared-relu experts in 8 "
                                "groups, top 6, expert ff 1024, gated shared ff 2048", "prompt_tokens": tokens,
                       "l2": "weights of one step (about 1.3 GB) exceed L2"}}

@@ -318,7 +318,7 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ 
 }
 
 // One block per token row.  x (fp32) += y_mult * y (y may be null); then h = x / sqrt(mean(x^2) + eps) * (w_shift + w) if h is given
-// (w_shift 1: a weight stored around zero).  h may be x itself when y is null and dt_h is fp32 (a norm in place).
+// (w_shift 1: w holds the offset from one).  h may be x itself when y is null and dt_h is fp32 (a norm in place).
 __global__ void __launch_bounds__(256) residual_scale_rms_kernel(float* x, const float* __restrict__ y, float y_mult,
                                                                  const float* __restrict__ w, float w_shift, void* h, int dt_h, int W,
                                                                  float eps) {

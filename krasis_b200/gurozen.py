@@ -1,5 +1,5 @@
 """Gurozen: a decoder-only design of pre-normed layers, x <- x + m mixer(norm1(x)), x <- x + m ff(norm2(x)) with one residual multiplier
-m and RMS norms whose weights are stored around zero (x / rms(x) * (1 + w)).  The embedding output is normed; the output head is the
+m and RMS norms whose weight tensors hold the offset from one (x / rms(x) * (1 + w)).  The embedding output is normed; the output head is the
 embedding table again, times a logit scale.
 
 Mixers:
@@ -36,8 +36,8 @@ from . import seqops as ops
 from .attention import HeadKVCache, RecurrentStatePool
 from .mixers import ChannelDeltaMixer, GatedMLP, MultiMapAttention, RoutedExperts, lin, llama3_table
 
-NORM_SHIFT = 1.0          # norm weights are stored around zero
-GROUP_MEMBERS = "top2"    # a group of experts is scored by the sum of its two largest scores
+NORM_SHIFT = 1.0          # a norm's weight tensor holds the offset from one
+GROUP_MEMBERS = "top2"    # an expert group competes with its best two members added up
 
 
 @dataclass

@@ -143,7 +143,7 @@ def squared_relu_expert(h, up, down):
 
 
 def route(h, router_w, rt):
-    """(chosen experts [T, top], their weights [T, top]): sigmoid scores, best groups by the sum of their two largest scores, top-k
+    """(chosen experts [T, top], their weights [T, top]): sigmoid scores, groups ranked by their best two members added up, top-k
     among the kept groups (ties to the lower index), weights renormalised and scaled."""
     T = h.shape[0]
     E, top = rt["experts"], rt["top"]

@@ -44,7 +44,7 @@ def dense(ff=56):
     return {"kind": "dense", "ff": ff}
 
 
-def moe(experts=12, top=3, groups=4, keep=2, ff=24, shared=40, scale=1.5):
+def moe(experts=16, top=3, groups=4, keep=2, ff=24, shared=40, scale=1.5):
     m = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": scale, "groups": {"count": groups, "keep": keep}}}
     if shared:
         m["shared"] = {"ff": shared}
