@@ -458,20 +458,23 @@ def test_other_sizes_and_degenerate_values(seq, layers, loop):
 
 
 def test_bfloat16_serving_close_to_oracle(seq):
-    """bfloat16 weights, GEMM inputs and cache.  A router choice between two experts whose scores differ by less than the rounding of
-    bfloat16 may fall the other way and moves that one position a lot, so the bound is on four positions out of five."""
-    raw = model_cfg(default_layers())
-    model, w = build(raw, dtype=torch.bfloat16, seed=14, page_size=4)
+    """bfloat16 weights, GEMM inputs and cache.  With dense feed-forwards every position is bounded.  With routed experts a choice
+    between two experts whose scores differ by less than the rounding of bfloat16 may fall the other way; that moves the position a lot
+    and, through the keys and the recurrent state, the ones after it, so there the bound is on the median position."""
     tk = toks(40, 50, 2)
-    want = O.forward(raw, w, tk)
-    a, b = run_portions(model, tk, [40]), run_portions(model, tk, [9, 2, 13])
+    dense_layers = [dict(L, mlp=dense(ff=40) if L["mlp"] else None) for L in default_layers()]
+    for layers, stat, what in ((dense_layers, np.max, "dense"), (default_layers(), np.median, "experts")):
+        raw = model_cfg(layers)
+        model, w = build(raw, dtype=torch.bfloat16, seed=14, page_size=4)
+        want = O.forward(raw, w, tk)
+        a, b = run_portions(model, tk, [40]), run_portions(model, tk, [9, 2, 13])
 
-    def most(got, ref, rel, what):
-        err = np.abs(got.astype(np.float64) - ref).max(-1) / np.abs(ref).max()
-        assert np.quantile(err, 0.8) <= rel, f"{what}: {np.quantile(err, 0.8):.3e}"
-    most(a, want, 6e-2, "bf16 whole")
-    most(b, want, 6e-2, "bf16 portions")
-    most(b, a.astype(np.float64), 6e-2, "bf16: portions against whole")
+        def bound(got, ref, rel, name):
+            err = stat(np.abs(got.astype(np.float64) - ref).max(-1)) / np.abs(ref).max()
+            assert err <= rel, f"{what}, {name}: {err:.3e}"
+        bound(a, want, 6e-2, "bf16 whole")
+        bound(b, want, 6e-2, "bf16 portions")
+        bound(b, a.astype(np.float64), 6e-2, "bf16: portions against whole")
 
 
 def test_tensor_core_prefill_of_capped_attention_and_experts(seq):
