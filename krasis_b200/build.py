@@ -3,8 +3,9 @@
 Two targets, so that a model only compiles what it runs on:
   "core"  libkrasis_b200.so       MoE prefill path: grouped / dense tcgen05 GEMMs, Gated DeltaNet, GQA / MLA attention, NCCL glue
   "seq"   libkrasis_b200_seq.so   ragged-batch sequence operators (csrc/seq_ops.cu, seq_mix.cu): norms, generic GEMM, windowed latent
-                                  attention with a sink, short convolution + gated delta rule with state slots, per-head paged
-                                  multi-map attention, gated linear units, router and routed experts
+                                  attention with a sink, short convolution + gated delta rule (decay per head or per key channel)
+                                  with state slots, per-head paged multi-map attention with an optional score cap, gated and
+                                  ungated linear units, router and routed experts
 nvcc cross-compiles without a GPU.  The .so files are git-ignored; a missing or stale one is rebuilt on demand.
 """
 import hashlib

@@ -1,18 +1,22 @@
 // Ragged-batch sequence operators, second part: per-head key/value caches, multi-map (differential) attention over a page list with
 // a causal mask that may be cut into chunks and / or a sliding window, gated linear units, and routed experts.
 //
-//   head_kv_prep           bias, per-vector RMS norm and interleaved rotary positions on the query and key vectors of every head and
-//                          map; keys and values go to the paged cache rows of the tokens' positions
+//   head_kv_prep           bias, RMS norm (per vector, or one over the whole of q and one over the whole of k) and rotary positions
+//                          (pairs 2i / 2i + 1, or i / i + dims / 2) on the query and key vectors of every head and map; keys and
+//                          values go to the paged cache rows of the tokens' positions
 //   paged_attn             softmax attention of every (head, map) query vector over the cached keys of its key/value head; the maps of
 //                          a head have keys of their own and share the values; keys j <= i of the same chunk and inside the window;
+//                          optional tanh cap on the scaled scores;
 //                          for steps of few tokens the key range is cut into pieces that run as separate blocks
 //   attn_finish            merges the pieces, combines the maps with per-map coefficients (differential attention: 1, -lambda),
 //                          unit RMS norm per head, output gate sigmoid(g) per head
-//   glu                    act(gate) * up in three flavours (tanh-GELU, SiLU, clamped swish with up + 1)
-//   route_topk             scores (softmax or sigmoid) -> + correction -> best groups -> top-k -> weights
+//   glu                    act(gate) * up in three flavours (tanh-GELU, SiLU, clamped swish with up + 1), or relu^2 without an up half
+//   route_topk             scores (softmax or sigmoid) -> + correction -> best groups (by their best or two best members) -> top-k
+//                          -> weights
 //   moe_bin / moe_gemm / moe_gemv / moe_combine
 //                          tokens binned per expert in tiles of 64 rows, tile GEMMs that pick their expert's weights, a GEMV form for
 //                          steps of few tokens, and the weighted sum over a token's experts (identity experts return the input)
+//                          plus the shared expert's rows, optionally times a per-token sigmoid gate
 //
 // Precision: scores, softmax, norms, rotary angles, router and every accumulation are fp32; `dt` selects storage only.
 #include "seq_common.cuh"
