@@ -81,7 +81,8 @@ KB2SEQ_API int kb2_seq_residual_scale_rms(float* x, const float* y, float y_mult
 
 /* gated delta rule over each sequence's portion; state [slots][H][dk][dv] fp32 is read and written back.
  * scratch (fp32, 2 T Hk dk + 2 T H + T H dv + 4 elements, 16-byte aligned) selects the register-state kernels when dk is 32, 64 or
- * 128 and dv a multiple of 32; with scratch == NULL, or other sizes, one block per (sequence, head) keeps the state in shared memory. */
+ * 128 and dv a multiple of 32; with scratch == NULL, or other sizes, one block per (sequence, head) keeps the state in shared memory
+ * (a state too large for that is cut into slices of value columns, one block each; this needs scratch). */
 KB2SEQ_API int kb2_seq_delta_rule(const float* conv, int C, const float* proj, long long ldp, int g_off, int a_off, int b_off, int T,
                                   int S, int H, int Hk, int dk, int dv, const float* A_log, const float* dt_bias, const float* norm_w,
                                   float eps, float* state, const int* cu, const int* slots, float* scratch, void* out, int dt_out,

@@ -692,20 +692,24 @@ __global__ void __launch_bounds__(1024) delta_rule_kernel(const float* __restric
                                                           int dk, int dv, const float* __restrict__ A_log,
                                                           const float* __restrict__ dt_bias, const float* __restrict__ norm_w, float eps,
                                                           float* __restrict__ state, const int* __restrict__ cu,
-                                                          const int* __restrict__ slots, void* __restrict__ out, int dt_out) {
+                                                          const int* __restrict__ slots, void* __restrict__ out, int dt_out, int dvb,
+                                                          float* __restrict__ o_raw) {
+  // dvb = value columns of this block (the columns of the state do not meet in the recurrence).  dvb < dv: blockIdx.z picks the slice,
+  // the raw read-out goes to o_raw [T, H, dv] and the norm and gate are left to delta_out_kernel.
   extern __shared__ float sm[];
-  float* S = sm;                                  // [dk][dv]
-  float* qn = S + (long long)dk * dv;             // [tile][dk]
+  float* S = sm;                                  // [dk][dvb]
+  float* qn = S + (long long)dk * dvb;            // [tile][dk]
   float* kn = qn + kDeltaTile * dk;               // [tile][dk]
-  float* ob = kn + kDeltaTile * dk;               // [tile][dv]
-  float* beta = ob + kDeltaTile * dv;             // [tile]
+  float* ob = kn + kDeltaTile * dk;               // [tile][dvb]
+  float* beta = ob + kDeltaTile * dvb;            // [tile]
   float* dec = beta + kDeltaTile;                 // [tile] or [tile][dk]
   const int dstr = ch ? dk : 1;
   const int s = blockIdx.x, h = blockIdx.y, hk = h / (H / Hk);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
   const int t0 = cu[s], n = cu[s + 1] - cu[s];
-  float* Sg = state + ((long long)slots[s] * H + h) * dk * dv;
-  for (int i = tid; i < dk * dv; i += blockDim.x) S[i] = Sg[i];
+  const int col0 = blockIdx.z * dvb, nc = min(dvb, dv - col0);
+  float* Sg = state + ((long long)slots[s] * H + h) * dk * dv + col0;
+  for (int i = tid; i < dk * nc; i += blockDim.x) S[(i / nc) * dvb + i % nc] = Sg[(long long)(i / nc) * dv + i % nc];
   const double rate_h = exp((double)A_log[h]);
   const float qscale = 1.f / sqrtf((float)dk);
   const int q_col = hk * dk, k_col = Hk * dk + hk * dk, v_col = 2 * Hk * dk + h * dv;
@@ -732,29 +736,30 @@ __global__ void __launch_bounds__(1024) delta_rule_kernel(const float* __restric
       if (lane == 0) beta[tt] = 1.f / (1.f + expf(-bproj[(long long)(t0 + b0 + tt) * ldb + h]));
     }
     __syncthreads();
-    if (tid < dv) {
+    if (tid < nc) {
       for (int tt = 0; tt < nt; ++tt) {
         const float* gg = dec + tt * dstr;
         const float* kk = kn + tt * dk;
         const float* qq = qn + tt * dk;
         float sk = 0.f;
         for (int i = 0; i < dk; ++i) {
-          const float sv = S[i * dv + tid] * gg[ch ? i : 0];
-          S[i * dv + tid] = sv;
+          const float sv = S[i * dvb + tid] * gg[ch ? i : 0];
+          S[i * dvb + tid] = sv;
           sk = fmaf(sv, kk[i], sk);
         }
-        const float u = beta[tt] * (conv[(long long)(t0 + b0 + tt) * C + v_col + tid] - sk);
+        const float u = beta[tt] * (conv[(long long)(t0 + b0 + tt) * C + v_col + col0 + tid] - sk);
         float o = 0.f;
         for (int i = 0; i < dk; ++i) {
-          const float sv = fmaf(kk[i], u, S[i * dv + tid]);
-          S[i * dv + tid] = sv;
+          const float sv = fmaf(kk[i], u, S[i * dvb + tid]);
+          S[i * dvb + tid] = sv;
           o = fmaf(sv, qq[i], o);
         }
-        ob[tt * dv + tid] = o;
+        if (o_raw != nullptr) o_raw[((long long)(t0 + b0 + tt) * H + h) * dv + col0 + tid] = o;
+        else ob[tt * dvb + tid] = o;
       }
     }
     __syncthreads();
-    for (int tt = warp; tt < nt; tt += nw) {
+    for (int tt = warp; o_raw == nullptr && tt < nt; tt += nw) {
       float ss = 0.f;
       for (int j = lane; j < dv; j += 32) ss += ob[tt * dv + j] * ob[tt * dv + j];
       ss = warp_sum(ss);
@@ -767,7 +772,7 @@ __global__ void __launch_bounds__(1024) delta_rule_kernel(const float* __restric
     }
   }
   __syncthreads();
-  for (int i = tid; i < dk * dv; i += blockDim.x) Sg[i] = S[i];
+  for (int i = tid; i < dk * nc; i += blockDim.x) Sg[(long long)(i / nc) * dv + i % nc] = S[(i / nc) * dvb + i % nc];
 }
 
 
@@ -1168,16 +1173,30 @@ static int delta_rule_launch(const float* conv, int C, const float* bproj, long 
     SEQ_LAUNCHED();
     return KB2SEQ_OK;
   }
-  if (dv > 1024) return failf(KB2SEQ_ERR_VALUE, "delta_rule: value size %d > 1024", dv);
-  const size_t smem = ((size_t)dk * dv + (size_t)kDeltaTile * (2 * dk + dv + 1 + (ch ? dk : 1))) * 4;
-  if (smem > 220 * 1024) return failf(KB2SEQ_ERR_VALUE, "delta_rule: a %d x %d state does not fit one block's shared memory", dk, dv);
+  auto smem_of = [&](int cols) { return ((size_t)dk * cols + (size_t)kDeltaTile * (2 * dk + cols + 1 + (ch ? dk : 1))) * 4; };
+  int dvb = dv;                                // a state too large for one block's shared memory is cut into slices of value columns
+  if (dv > 1024 || smem_of(dv) > 220 * 1024) {
+    dvb = dv < 1024 ? dv / 32 * 32 : 1024;
+    while (dvb > 32 && smem_of(dvb) > 220 * 1024) dvb -= 32;
+    if (dvb < 32 || smem_of(dvb) > 220 * 1024)
+      return failf(KB2SEQ_ERR_VALUE, "delta_rule: %d key channels do not fit one block's shared memory", dk);
+    if (!scratch) return failf(KB2SEQ_ERR_VALUE, "delta_rule: a %d x %d state needs the scratch buffer (T H dv floats)", dk, dv);
+  }
+  const size_t smem = smem_of(dvb);
   if (smem > 48 * 1024) SEQ_CUDA(cudaFuncSetAttribute(delta_rule_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  int threads = (dv + 31) / 32 * 32;
+  int threads = (dvb + 31) / 32 * 32;
   if (threads < 128) threads = 128;
-  dim3 grid(S, H);
+  const bool cut = dvb < dv;
+  dim3 grid(S, H, (dv + dvb - 1) / dvb);
   delta_rule_kernel<<<grid, threads, smem, (cudaStream_t)stream>>>(conv, C, bproj, ldb, aproj, lda, ch, gproj, ldg, gate_act, H, Hk, dk, dv, A_log,
-                                                                  dt_bias, norm_w, eps, state, cu, slots, out, dt_out);
+                                                                  dt_bias, norm_w, eps, state, cu, slots, out, dt_out, dvb,
+                                                                  cut ? scratch : nullptr);
   SEQ_LAUNCHED();
+  if (cut) {
+    const long long no = (long long)T * H;
+    delta_out_kernel<<<(unsigned)((no + 7) / 8), 256, 0, (cudaStream_t)stream>>>(scratch, gproj, ldg, gate_act, H, dv, norm_w, eps, T, out, dt_out);
+    SEQ_LAUNCHED();
+  }
   return KB2SEQ_OK;
 }
 

@@ -194,7 +194,7 @@ class GatedDeltaMixer:
                                         tb.seq_of.data_ptr(), tb.cu.data_ptr(), tb.slots.data_ptr(), conv.data_ptr(), s))
         o = torch.empty((T, self.H * self.dv), dtype=self.dtype, device=h.device)
         scratch = None
-        if self.register_state_kernel:
+        if self.register_state_kernel or self.dk * self.dv > 32768:      # a large state is cut into column slices that meet in scratch
             scratch = torch.empty(2 * T * self.Hk * self.dk + 2 * T * self.H + T * self.H * self.dv + 4, dtype=torch.float32, device=h.device)
         ops.check(lib.kb2_seq_delta_rule(conv.data_ptr(), self.C, proj.data_ptr(), proj.stride(0), self.g_off, self.a_off, self.b_off, T,
                                          tb.S, self.H, self.Hk, self.dk, self.dv, self.A_log.data_ptr(), self.dt_bias.data_ptr(),
@@ -253,7 +253,7 @@ class ChannelDeltaMixer:
         gate_in = self._second(proj, self.g_off, self.rg, self.w_g2)                # [T, H dv]
         o = torch.empty((T, H * self.dv), dtype=self.dtype, device=h.device)
         scratch = None
-        if self.register_state_kernel:
+        if self.register_state_kernel or self.dk * self.dv > 32768:      # a large state is cut into column slices that meet in scratch
             n = 2 * T * self.Hk * self.dk + T * H + T * H * self.dk + T * H * self.dv + 16
             scratch = torch.empty(n, dtype=torch.float32, device=h.device)
         beta_in = proj[:, self.b_off:]

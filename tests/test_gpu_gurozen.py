@@ -229,7 +229,7 @@ def run_delta(seq, mixer, h, cuts, slot=2):
 
 @pytest.mark.parametrize("m", [delta(), delta(heads=3, kv_heads=3, dim=32, vdim=32, conv=2), delta(heads=4, kv_heads=1, dim=64, vdim=64, conv=3),
                                delta(heads=2, kv_heads=1, dim=128, vdim=32, conv=4), delta(heads=1, kv_heads=1, dim=5, vdim=3, conv=1),
-                               delta(heads=6, kv_heads=2, dim=20, vdim=70, conv=6)])
+                               delta(heads=6, kv_heads=2, dim=20, vdim=70, conv=6), delta(heads=2, kv_heads=1, dim=256, vdim=250, conv=2)])
 def test_channel_delta_alone(seq, m):
     from krasis_b200.mixers import ChannelDeltaMixer
     W, T = 40, 37
