@@ -443,19 +443,34 @@ class HeadKVCache(PagedKVCache):
     [max_pages, page_size, key_width] (all key/value heads and maps of a token side by side, after norm and rotation) and one of values
     [max_pages, page_size, value_width], in the serving dtype (bfloat16 or float32).  Layers may differ in their widths and share one
     page numbering; a layer that reads another layer's keys and values is given that layer's pools (`layer_offset` of the source).
-    Allocation is the free list of `PagedKVCache`."""
+    Allocation is the free list of `PagedKVCache`.
+
+    A layer whose dims carry a third entry `pool` also gets pooled pools: the mean key and mean value of every block of `pool`
+    consecutive positions, [max_pages, ceil(page_size / pool), width] each, under the same page numbering (a block lies in the page of
+    its last position), so they are freed and reused with the pages.  A latent-attention layer fits the same pools with the latent as
+    its "keys" and the shared rotated key part as its "values"."""
 
     def __init__(self, layer_dims, device, max_pages: int, dtype=torch.bfloat16, page_size: int = 64):
         if dtype not in (torch.bfloat16, torch.float32):
             raise ValueError("cache dtype: bfloat16 or float32")
         self.num_layers, self.page_size, self.kv_dtype, self.max_pages = len(layer_dims), page_size, dtype, max_pages
         self.device = torch.device(device)
-        self.k = [torch.zeros((max_pages, page_size, kw), dtype=dtype, device=self.device) for kw, _ in layer_dims]
-        self.v = [torch.zeros((max_pages, page_size, vw), dtype=dtype, device=self.device) for _, vw in layer_dims]
+        self.k = [torch.zeros((max_pages, page_size, max(dims[0], 1)), dtype=dtype, device=self.device) for dims in layer_dims]
+        self.v = [torch.zeros((max_pages, page_size, max(dims[1], 1)), dtype=dtype, device=self.device) for dims in layer_dims]
+        self.kp, self.vp = [], []
+        for dims in layer_dims:
+            pool = dims[2] if len(dims) > 2 else 0
+            rows = (page_size + pool - 1) // pool if pool else 0
+            self.kp.append(torch.zeros((max_pages, rows, dims[0]), dtype=dtype, device=self.device) if pool else None)
+            self.vp.append(torch.zeros((max_pages, rows, dims[1]), dtype=dtype, device=self.device) if pool else None)
         self._free = list(range(max_pages - 1, -1, -1))
 
     def get_layer_caches(self, layer_offset: int):
         return self.k[layer_offset], self.v[layer_offset]
+
+    def get_pooled_caches(self, layer_offset: int):
+        """(mean keys, mean values) of the layer's blocks, or None for a layer without pooled blocks."""
+        return (self.kp[layer_offset], self.vp[layer_offset]) if self.kp[layer_offset] is not None else None
 
 
 class RecurrentStatePool:

@@ -2,10 +2,11 @@
 
 Two targets, so that a model only compiles what it runs on:
   "core"  libkrasis_b200.so       MoE prefill path: grouped / dense tcgen05 GEMMs, Gated DeltaNet, GQA / MLA attention, NCCL glue
-  "seq"   libkrasis_b200_seq.so   ragged-batch sequence operators (csrc/seq_ops.cu, seq_mix.cu): norms, generic GEMM, windowed latent
-                                  attention with a sink, short convolution + gated delta rule (decay per head or per key channel)
-                                  with state slots, per-head paged multi-map attention with an optional score cap, gated and
-                                  ungated linear units, router and routed experts
+  "seq"   libkrasis_b200_seq.so   ragged-batch sequence operators (csrc/seq_ops.cu, seq_mix.cu, seq_rec.cu): norms, generic GEMM, windowed
+                                  latent attention with an optional sink, short convolution + gated delta rule (decay per head or per
+                                  key channel) with state slots, per-head paged multi-map attention (score cap, sink, pooled blocks
+                                  before the window, rotated values), gated and ungated linear units, router and routed experts,
+                                  gated linear attention and selective scan with state slots, side-by-side mixers, depth average
 nvcc cross-compiles without a GPU.  The .so files are git-ignored; a missing or stale one is rebuilt on demand.
 """
 import hashlib
@@ -18,7 +19,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "_lib")
 LIB = os.path.join(LIBDIR, "libkrasis_b200.so")
 SEQ_LIB = os.path.join(LIBDIR, "libkrasis_b200_seq.so")
-SEQ_SOURCES = ["seq_ops.cu", "seq_mix.cu"]
+SEQ_SOURCES = ["seq_ops.cu", "seq_mix.cu", "seq_rec.cu"]
 SOURCES = ["grouped_gemm.cu", "router_gemm.cu", "dense_gemm.cu", "gdn.cu", "gdn_tc.cu", "gqa.cu", "elementwise.cu", "moe_kernels.cu", "capi.cu", "capi_attn.cu", "capi_comm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

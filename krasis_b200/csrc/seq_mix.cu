@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(256) head_kv_prep_kernel(float* __restrict__ p
                                                            int rot_dims, const int* __restrict__ positions,
                                                            const int* __restrict__ seq_of, const int* __restrict__ pages, int max_pages,
                                                            int page_size, void* __restrict__ kc, void* __restrict__ vc, int dt_cache,
-                                                           int norm_whole, int rot_half) {
+                                                           int norm_whole, int rot_half, const double* __restrict__ vfreq) {
   extern __shared__ float rot_tab[];          // [rot_dims / 2][2]: cos, sin of the token's position, shared by all its vectors
   __shared__ float red[32];
   const long long t = blockIdx.x;
@@ -103,8 +103,57 @@ __global__ void __launch_bounds__(256) head_kv_prep_kernel(float* __restrict__ p
     }
   }
   const long long v0 = (long long)nvec * d;
-  for (int i = threadIdx.x; i < G * dv; i += blockDim.x)
-    st_dt(vc, dt_cache, slot * G * dv + i, p[v0 + i] + (bias ? bias[v0 + i] : 0.f));
+  if (vfreq == nullptr) {
+    for (int i = threadIdx.x; i < G * dv; i += blockDim.x)
+      st_dt(vc, dt_cache, slot * G * dv + i, p[v0 + i] + (bias ? bias[v0 + i] : 0.f));
+    return;
+  }
+  // rotated values: every pair of the value vector turns by position * vfreq[pair], in the pair layout of the keys
+  const int vh = dv >> 1;
+  for (int i = threadIdx.x; i < G * vh; i += blockDim.x) {
+    const int g = i / vh, j = i - g * vh;
+    const int iu = rot_half ? j : 2 * j, iv = rot_half ? j + vh : 2 * j + 1;
+    const long long b0 = v0 + (long long)g * dv;
+    const float u = p[b0 + iu] + (bias ? bias[b0 + iu] : 0.f), v = p[b0 + iv] + (bias ? bias[b0 + iv] : 0.f);
+    float c, sn;
+    rot_cs(pos, vfreq[j], 1.f, &c, &sn);
+    st_dt(vc, dt_cache, (slot * G + g) * dv + iu, u * c - v * sn);
+    st_dt(vc, dt_cache, (slot * G + g) * dv + iv, v * c + u * sn);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ pooled blocks
+// A block of `pool` consecutive positions b pool .. b pool + pool - 1 is summarised by the mean of its cached keys and the mean of its
+// cached values.  The summary of block b lives in the page of the block's last position: pooled pools have rows_per_page =
+// ceil(page_size / pool) rows per page, and block b is row b - floor(page first position / pool) of that page.
+__device__ __forceinline__ long long pooled_row(int b, int pool, int page_size, int rows_per_page, const int* __restrict__ seq_pages) {
+  const int pg = (b * pool + pool - 1) / page_size;
+  return (long long)seq_pages[pg] * rows_per_page + (b - pg * page_size / pool);
+}
+
+// One block per token of the step; only a token that completes a block works: it averages the block's cache rows (fp32, in position
+// order) into the pooled pools.  Runs after head_kv_prep of the same step.
+__global__ void __launch_bounds__(256) kv_pool_kernel(const void* __restrict__ kc, const void* __restrict__ vc, void* __restrict__ kp,
+                                                      void* __restrict__ vp, int dt_cache, int kw, int vw, int pool, int rows_per_page,
+                                                      const int* __restrict__ positions, const int* __restrict__ seq_of,
+                                                      const int* __restrict__ pages, int max_pages, int page_size) {
+  const long long t = blockIdx.x;
+  const int pos = positions[t];
+  if (pos % pool != pool - 1) return;
+  const int* sp = pages + (long long)seq_of[t] * max_pages;
+  const long long dst = pooled_row(pos / pool, pool, page_size, rows_per_page, sp);
+  const float inv = 1.f / (float)pool;
+  for (int i = threadIdx.x; i < kw + vw; i += blockDim.x) {
+    const bool is_k = i < kw;
+    const int c = is_k ? i : i - kw, wdt = is_k ? kw : vw;
+    const void* src = is_k ? kc : vc;
+    float acc = 0.f;
+    for (int j = pos - pool + 1; j <= pos; ++j) {
+      const long long row = (long long)sp[j / page_size] * page_size + j % page_size;
+      acc += ld_dt(src, dt_cache, row * wdt + c);
+    }
+    st_dt(is_k ? kp : vp, dt_cache, dst * wdt + c, acc * inv);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------ attention over the page list
@@ -115,7 +164,8 @@ __global__ void __launch_bounds__(kPAThreads) paged_attn_kernel(
     const float* __restrict__ proj, long long ldp, int H, int G, int M, int d, int dv, int RB, const void* __restrict__ kc,
     const void* __restrict__ vc, int dt_cache, const int* __restrict__ positions, const int* __restrict__ seq_of,
     const int* __restrict__ pages, int max_pages, int page_size, float scale, int chunk, int window, float* __restrict__ out, int nsplit,
-    float* __restrict__ part_acc, float* __restrict__ part_ml, const int* __restrict__ cu, int skip_from, float softcap) {
+    float* __restrict__ part_acc, float* __restrict__ part_ml, const int* __restrict__ cu, int skip_from, float softcap,
+    const float* __restrict__ sinks, int pool, int rows_per_page, const void* __restrict__ kp, const void* __restrict__ vp) {
   extern __shared__ __align__(16) float sm[];
   constexpr int KT = kPAKT;
   const long long t = blockIdx.x;
@@ -138,28 +188,39 @@ __global__ void __launch_bounds__(kPAThreads) paged_attn_kernel(
     const int r = i / d, dd = i - r * d;
     qs[i] = proj[t * ldp + ((long long)g * R + r0 + r) * d + dd];
   }
-  if (tid < nr) {
-    m_run[tid] = -INFINITY;
-    l_run[tid] = 0.f;
+  const int z = blockIdx.z;
+  if (tid < nr) {          // a sink is a key without a value: the running maximum starts at it, the running sum at 1 (first piece only)
+    const bool sk = sinks != nullptr && z == 0;
+    m_run[tid] = sk ? sinks[g * (H / G) + (r0 + tid) / M] : -INFINITY;
+    l_run[tid] = sk ? 1.f : 0.f;
   }
   float acc[kPAAcc];
 #pragma unroll
   for (int a = 0; a < kPAAcc; ++a) acc[a] = 0.f;
   int j_lo = max(0, pos - window + 1);
   if (chunk > 0) j_lo = max(j_lo, pos / chunk * chunk);
-  int j_begin = j_lo, j_end = pos;
-  const int z = blockIdx.z;
+  // the keys of a token, in order: the pooled blocks that lie wholly before the window (block b: b pool + pool - 1 <= pos - window),
+  // then the positions j_lo .. pos.  Index u of that list: u < nb is block u, else position j_lo + u - nb.
+  const int nb = pool > 0 ? max(0, pos - window + 1) / pool : 0;
+  const int total = nb + pos - j_lo + 1;
+  int u_begin = 0, u_end = total - 1;
   if (nsplit > 1) {
-    const int piece = (((pos - j_lo + 1) + nsplit - 1) / nsplit + KT - 1) / KT * KT;
-    j_begin = j_lo + z * piece;
-    j_end = min(pos, j_begin + piece - 1);
+    const int piece = ((total + nsplit - 1) / nsplit + KT - 1) / KT * KT;
+    u_begin = z * piece;
+    u_end = min(total - 1, u_begin + piece - 1);
   }
-  for (int j0 = j_begin; j0 <= j_end; j0 += KT) {
-    const int nk = min(KT, j_end - j0 + 1);
+  const int* sp = pages + (long long)seq * max_pages;
+  for (int j0 = u_begin; j0 <= u_end; j0 += KT) {
+    const int nk = min(KT, u_end - j0 + 1);
     __syncthreads();
     if (tid < nk) {
-      const int j = j0 + tid;
-      krow[tid] = (long long)pages[(long long)seq * max_pages + j / page_size] * page_size + j % page_size;
+      const int u = j0 + tid;
+      if (u < nb) {
+        krow[tid] = -1 - pooled_row(u, pool, page_size, rows_per_page, sp);      // negative: a row of the pooled pools
+      } else {
+        const int j = j_lo + u - nb;
+        krow[tid] = (long long)sp[j / page_size] * page_size + j % page_size;
+      }
     }
     __syncthreads();
     if (dt_cache == 1 && (KD & 7) == 0 && (dv & 7) == 0) {
@@ -167,12 +228,14 @@ __global__ void __launch_bounds__(kPAThreads) paged_attn_kernel(
       for (int i = tid; i < nk * (K8 + V8); i += kPAThreads) {
         const int k = i / (K8 + V8), c = i - k * (K8 + V8);
         float f[8];
+        const bool pooled = krow[k] < 0;
+        const long long row = pooled ? -1 - krow[k] : krow[k];
         if (c < K8) {
-          unpack8(*reinterpret_cast<const uint4*>((const bf16*)kc + (krow[k] * G + g) * KD + c * 8), f);
+          unpack8(*reinterpret_cast<const uint4*>((const bf16*)(pooled ? kp : kc) + (row * G + g) * KD + c * 8), f);
 #pragma unroll
           for (int e = 0; e < 8; ++e) kt[k * KP + c * 8 + e] = f[e];
         } else {
-          unpack8(*reinterpret_cast<const uint4*>((const bf16*)vc + (krow[k] * G + g) * dv + (c - K8) * 8), f);
+          unpack8(*reinterpret_cast<const uint4*>((const bf16*)(pooled ? vp : vc) + (row * G + g) * dv + (c - K8) * 8), f);
 #pragma unroll
           for (int e = 0; e < 8; ++e) vt[k * dv + (c - K8) * 8 + e] = f[e];
         }
@@ -180,11 +243,13 @@ __global__ void __launch_bounds__(kPAThreads) paged_attn_kernel(
     } else {
       for (int i = tid; i < nk * KD; i += kPAThreads) {
         const int k = i / KD, c = i - k * KD;
-        kt[k * KP + c] = ld_dt(kc, dt_cache, (krow[k] * G + g) * KD + c);
+        const bool pooled = krow[k] < 0;
+        kt[k * KP + c] = ld_dt(pooled ? kp : kc, dt_cache, ((pooled ? -1 - krow[k] : krow[k]) * G + g) * KD + c);
       }
       for (int i = tid; i < nk * dv; i += kPAThreads) {
         const int k = i / dv, c = i - k * dv;
-        vt[i] = ld_dt(vc, dt_cache, (krow[k] * G + g) * dv + c);
+        const bool pooled = krow[k] < 0;
+        vt[i] = ld_dt(pooled ? vp : vc, dt_cache, ((pooled ? -1 - krow[k] : krow[k]) * G + g) * dv + c);
       }
     }
     __syncthreads();
@@ -249,7 +314,9 @@ __global__ void __launch_bounds__(256) attn_finish_kernel(const float* __restric
                                                           const float* __restrict__ coef, int unit_norm, float eps, float post_scale,
                                                           const float* __restrict__ gate, long long ldg, void* __restrict__ out,
                                                           int dt_out, const int* __restrict__ seq_of, const int* __restrict__ cu,
-                                                          int skip_from) {
+                                                          int skip_from, int gate_wide, const int* __restrict__ positions,
+                                                          const double* __restrict__ vfreq, int rot_half) {
+  __shared__ float turn_buf[8][32 * kFinAcc];
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (w >= T * H) return;
@@ -309,11 +376,37 @@ __global__ void __launch_bounds__(256) attn_finish_kernel(const float* __restric
     ss = warp_sum(ss);
     f = post_scale / sqrtf(ss / (float)dv + eps);
   }
-  if (gate != nullptr) f *= 1.f / (1.f + expf(-gate[t * ldg + h]));
+  if (vfreq != nullptr) {       // values were cached rotated by their positions: turn the sum back by the query's position
+    float* tb = turn_buf[threadIdx.x >> 5];
+#pragma unroll
+    for (int i = 0; i < kFinAcc; ++i) {
+      const int c = lane + 32 * i;
+      if (c < dv) tb[c] = o[i];
+    }
+    __syncwarp();
+    const int vh = dv >> 1, pos = positions[t];
+#pragma unroll
+    for (int i = 0; i < kFinAcc; ++i) {
+      const int c = lane + 32 * i;
+      if (c < dv) {
+        const int j = rot_half ? (c < vh ? c : c - vh) : c >> 1;
+        const bool first = rot_half ? c < vh : !(c & 1);
+        const float other = tb[rot_half ? (first ? c + vh : c - vh) : c ^ 1];
+        float cs, sn;
+        rot_cs(pos, vfreq[j], 1.f, &cs, &sn);
+        o[i] = first ? o[i] * cs + other * sn : o[i] * cs - other * sn;      // the turn by -pos * f
+      }
+    }
+  }
+  if (gate != nullptr && !gate_wide) f *= 1.f / (1.f + expf(-gate[t * ldg + h]));
 #pragma unroll
   for (int i = 0; i < kFinAcc; ++i) {
     const int c = lane + 32 * i;
-    if (c < dv) st_dt(out, dt_out, w * dv + c, o[i] * f);
+    if (c < dv) {
+      float v = o[i] * f;
+      if (gate != nullptr && gate_wide) v *= 1.f / (1.f + expf(-gate[t * ldg + (long long)h * dv + c]));
+      st_dt(out, dt_out, w * dv + c, v);
+    }
   }
 }
 
@@ -650,13 +743,25 @@ extern "C" {
 KB2SEQ_API int kb2_seq_head_kv_prep(float* proj, long long ldp, int T, int H, int G, int M, int d, int dv, const float* bias,
                                     const float* qw, const float* kw, float eps, const double* freq, int rot_dims, const int* positions,
                                     const int* seq_of, const int* pages, int max_pages, int page_size, void* kc, void* vc, int dt_cache,
-                                    int norm_whole, int rot_half, void* stream) {
+                                    int norm_whole, int rot_half, const double* vfreq, void* stream) {
+  if (vfreq && (dv & 1)) return failf(KB2SEQ_ERR_VALUE, "head_kv_prep: rotated values need an even value size");
   if (!proj || !positions || !seq_of || !pages || T <= 0 || H <= 0 || G < 0 || M <= 0 || d <= 0 || dv < 0 || rot_dims < 0 ||
       rot_dims > d || (rot_dims & 1) || (rot_dims && !freq) || page_size <= 0 || max_pages <= 0 || bad_dt(dt_cache) ||
       (G > 0 && (!kc || !vc)))
     return failf(KB2SEQ_ERR_VALUE, "head_kv_prep: bad argument");
   head_kv_prep_kernel<<<T, 256, (size_t)rot_dims * 4, (cudaStream_t)stream>>>(proj, ldp, H, G, M, d, dv, bias, qw, kw, eps, freq, rot_dims, positions, seq_of,
-                                                           pages, max_pages, page_size, kc, vc, dt_cache, norm_whole, rot_half);
+                                                           pages, max_pages, page_size, kc, vc, dt_cache, norm_whole, rot_half, vfreq);
+  SEQ_LAUNCHED();
+  return KB2SEQ_OK;
+}
+
+KB2SEQ_API int kb2_seq_kv_pool(const void* kc, const void* vc, void* kp, void* vp, int dt_cache, int kw, int vw, int pool, int T,
+                               const int* positions, const int* seq_of, const int* pages, int max_pages, int page_size, void* stream) {
+  if (!kc || !vc || !kp || !vp || bad_dt(dt_cache) || kw <= 0 || vw <= 0 || pool <= 0 || T <= 0 || !positions || !seq_of || !pages ||
+      max_pages <= 0 || page_size <= 0)
+    return failf(KB2SEQ_ERR_VALUE, "kv_pool: bad argument");
+  kv_pool_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(kc, vc, kp, vp, dt_cache, kw, vw, pool, (page_size + pool - 1) / pool, positions, seq_of,
+                                                      pages, max_pages, page_size);
   SEQ_LAUNCHED();
   return KB2SEQ_OK;
 }
@@ -664,7 +769,9 @@ KB2SEQ_API int kb2_seq_head_kv_prep(float* proj, long long ldp, int T, int H, in
 KB2SEQ_API int kb2_seq_paged_attn(const float* proj, long long ldp, int T, int H, int G, int M, int d, int dv, const void* kc,
                                   const void* vc, int dt_cache, const int* positions, const int* seq_of, const int* pages, int max_pages,
                                   int page_size, float scale, int chunk, int window, float* out, int nsplit, float* part_acc,
-                                  float* part_ml, const int* cu, int skip_from, float softcap, void* stream) {
+                                  float* part_ml, const int* cu, int skip_from, float softcap, const float* sinks, int pool, const void* kp,
+                                  const void* vp, void* stream) {
+  if (pool < 0 || (pool > 0 && (!kp || !vp || chunk > 0))) return failf(KB2SEQ_ERR_VALUE, "paged_attn: pooled blocks need their pools and no chunks");
   if (!proj || !kc || !vc || !positions || !seq_of || !pages || !out || T <= 0 || H <= 0 || G <= 0 || H % G || M <= 0 || d <= 0 ||
       dv <= 0 || window <= 0 || chunk < 0 || page_size <= 0 || bad_dt(dt_cache) || !(softcap >= 0.f))
     return failf(KB2SEQ_ERR_VALUE, "paged_attn: bad argument");
@@ -683,14 +790,16 @@ KB2SEQ_API int kb2_seq_paged_attn(const float* proj, long long ldp, int T, int H
   if ((long long)G * nrb > 65535) return failf(KB2SEQ_ERR_VALUE, "paged_attn: too many heads");
   paged_attn_kernel<<<dim3(T, G * nrb, nsplit), kPAThreads, smem, (cudaStream_t)stream>>>(
       proj, ldp, H, G, M, d, dv, RB, kc, vc, dt_cache, positions, seq_of, pages, max_pages, page_size, scale, chunk, window, out, nsplit,
-      part_acc, part_ml, cu, skip_from, softcap);
+      part_acc, part_ml, cu, skip_from, softcap, sinks, pool, pool > 0 ? (page_size + pool - 1) / pool : 0, kp, vp);
   SEQ_LAUNCHED();
   return KB2SEQ_OK;
 }
 
 KB2SEQ_API int kb2_seq_attn_finish(const float* a, const float* part_acc, const float* part_ml, int nsplit, int T, int H, int M, int dv,
                                    const float* coef, int unit_norm, float eps, float post_scale, const float* gate, long long ldg,
-                                   void* out, int dt_out, const int* seq_of, const int* cu, int skip_from, void* stream) {
+                                   void* out, int dt_out, const int* seq_of, const int* cu, int skip_from, int gate_wide,
+                                   const int* positions, const double* vfreq, int rot_half, void* stream) {
+  if (vfreq && (!positions || (dv & 1))) return failf(KB2SEQ_ERR_VALUE, "attn_finish: turning back needs positions and an even value size");
   if (!out || T <= 0 || H <= 0 || M <= 0 || dv <= 0 || bad_dt(dt_out) || nsplit < 1 || (nsplit == 1 && !a) ||
       (nsplit > 1 && (!part_acc || !part_ml)) || (cu && !seq_of))
     return failf(KB2SEQ_ERR_VALUE, "attn_finish: bad argument");
@@ -698,7 +807,7 @@ KB2SEQ_API int kb2_seq_attn_finish(const float* a, const float* part_acc, const 
   const long long nwarps = (long long)T * H;
   attn_finish_kernel<<<(unsigned)((nwarps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(a, part_acc, part_ml, nsplit, T, H, M, dv, coef, unit_norm,
                                                                                       eps, post_scale, gate, ldg, out, dt_out, seq_of, cu,
-                                                                                      skip_from);
+                                                                                      skip_from, gate_wide, positions, vfreq, rot_half);
   SEQ_LAUNCHED();
   return KB2SEQ_OK;
 }

@@ -385,13 +385,14 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(float* __restrict__ pr
                                                           const float* __restrict__ cw, float eps, const double* __restrict__ freq,
                                                           int rot_dims, float amp, const int* __restrict__ positions,
                                                           const int* __restrict__ seq_of, const int* __restrict__ pages, int max_pages,
-                                                          int page_size, void* __restrict__ ckv, void* __restrict__ kr, int dt_cache) {
+                                                          int page_size, void* __restrict__ ckv, void* __restrict__ kr, int dt_cache,
+                                                          const float* __restrict__ lat_rows, long long ldl) {
   __shared__ float red[32];
   const long long t = blockIdx.x;
   const int pos = positions[t];
   float* p = proj + t * ldp;
   const long long slot = (long long)pages[(long long)seq_of[t] * max_pages + pos / page_size] * page_size + pos % page_size;
-  const float* lat = p + (long long)H * (dn + dr);
+  const float* lat = lat_rows != nullptr ? lat_rows + t * ldl : p + (long long)H * (dn + dr);
   float ss = 0.f;
   for (int d = threadIdx.x; d < r; d += blockDim.x) ss += lat[d] * lat[d];
   ss = block_sum(ss, red);
@@ -456,8 +457,9 @@ __global__ void __launch_bounds__(kAttnThreads) latent_window_attn_kernel(
   // weighted latents) for latent_attn_combine_kernel; the sink belongs to piece 0
   const int z = blockIdx.z;
   if (tid < nh) {
-    m_run[tid] = z == 0 ? sinks[h0 + tid] : -INFINITY;
-    l_run[tid] = z == 0 ? 1.f : 0.f;
+    const bool sk = z == 0 && sinks != nullptr;       // no sinks: an ordinary softmax over the keys
+    m_run[tid] = sk ? sinks[h0 + tid] : -INFINITY;
+    l_run[tid] = sk ? 1.f : 0.f;
   }
   float acc[kAttnAcc];
 #pragma unroll
@@ -605,7 +607,7 @@ __global__ void __launch_bounds__(128) latent_attn_combine_kernel(const float* _
 __global__ void conv_silu_kernel(const float* __restrict__ proj, long long ldp, int C, int K, const float* __restrict__ taps,
                                  const float* __restrict__ tail, const int* __restrict__ seq_of, const int* __restrict__ cu,
                                  const int* __restrict__ slots, long long T, float* __restrict__ out, const float* __restrict__ bias,
-                                 int act) {
+                                 int act, int bias_after) {
   const long long t = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
@@ -613,8 +615,9 @@ __global__ void conv_silu_kernel(const float* __restrict__ proj, long long ldp, 
   const int s = seq_of[t];
   const int i = (int)(t - cu[s]);
   const float* tl = tail + ((long long)slots[s] * C + c) * (K - 1);
-  const float b = bias != nullptr ? bias[c] : 0.f;
-  float acc = 0.f;
+  const float bv = bias != nullptr ? bias[c] : 0.f;
+  const float b = bias_after ? 0.f : bv;       // bias_after: the bias joins the convolution's result, not its inputs
+  float acc = bias_after ? bv : 0.f;
   for (int j = 0; j < K; ++j) {
     const int src = i - (K - 1) + j;
     const float xv = src >= 0 ? proj[(t - i + src) * ldp + c] + b : tl[(K - 1) + src];
@@ -630,14 +633,15 @@ __global__ void __launch_bounds__(256) conv_run_kernel(const float* __restrict__
                                                        const float* __restrict__ taps, const float* __restrict__ tail,
                                                        const int* __restrict__ seq_of, const int* __restrict__ cu,
                                                        const int* __restrict__ slots, long long T, float* __restrict__ out,
-                                                       const float* __restrict__ bias, int act) {
+                                                       const float* __restrict__ bias, int act, int bias_after) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
   const long long r0 = (long long)blockIdx.y * kConvRun, r1 = min(T, r0 + kConvRun);
   float w[kConvMaxTaps], x[kConvMaxTaps] = {};     // x[j]: the input K - 1 - j rows back, x[K - 1] the current one
 #pragma unroll
   for (int j = 0; j < kConvMaxTaps; ++j) w[j] = j < K ? taps[(long long)c * K + j] : 0.f;
-  const float b = bias != nullptr ? bias[c] : 0.f;
+  const float bv = bias != nullptr ? bias[c] : 0.f;
+  const float b = bias_after ? 0.f : bv, b_out = bias_after ? bv : 0.f;
   int s = -1;
   for (long long t = r0; t < r1; ++t) {
     const int st = seq_of[t];
@@ -656,7 +660,7 @@ __global__ void __launch_bounds__(256) conv_run_kernel(const float* __restrict__
     for (int j = 0; j < kConvMaxTaps - 1; ++j) x[j] = x[j + 1];
     // after the shift x[0 .. K - 2] hold the K - 1 earlier inputs; the current one goes to x[K - 1]
     const float cur = proj[t * ldp + c] + b;
-    float acc = 0.f;
+    float acc = b_out;
 #pragma unroll
     for (int j = 0; j < kConvMaxTaps; ++j) {
       if (j == K - 1) x[j] = cur;
@@ -1060,12 +1064,13 @@ KB2SEQ_API int kb2_seq_side_gate(const float* g, const void* table, int dt_table
 
 KB2SEQ_API int kb2_seq_latent_prep(float* proj, long long ldp, int T, int H, int dn, int dr, int r, const float* cw, float eps,
                                    const double* freq, int rot_dims, float amp, const int* positions, const int* seq_of,
-                                   const int* pages, int max_pages, int page_size, void* ckv, void* kr, int dt_cache, void* stream) {
+                                   const int* pages, int max_pages, int page_size, void* ckv, void* kr, int dt_cache, const float* lat,
+                                   long long ldl, void* stream) {
   if (!proj || !cw || !freq || !positions || !seq_of || !pages || !ckv || !kr || T <= 0 || H <= 0 || dn < 0 || dr < 0 || r <= 0 ||
       rot_dims < 0 || rot_dims > dr || (rot_dims & 1) || page_size <= 0 || max_pages <= 0 || bad_dt(dt_cache))
     return failf(KB2SEQ_ERR_VALUE, "latent_prep: bad argument");
   latent_prep_kernel<<<T, 128, 0, (cudaStream_t)stream>>>(proj, ldp, H, dn, dr, r, cw, eps, freq, rot_dims, amp, positions, seq_of, pages,
-                                                          max_pages, page_size, ckv, kr, dt_cache);
+                                                          max_pages, page_size, ckv, kr, dt_cache, lat, ldl);
   SEQ_LAUNCHED();
   return KB2SEQ_OK;
 }
@@ -1075,7 +1080,7 @@ KB2SEQ_API int kb2_seq_latent_window_attn(const float* q_abs, const float* proj,
                                           const int* pages, int max_pages, int page_size, const float* sinks, float scale, int window,
                                           float* out, const int* cu, int skip_from, int nsplit, float* part_acc, float* part_ml,
                                           void* stream) {
-  if (!q_abs || !proj || !ckv || !kr || !positions || !seq_of || !pages || !sinks || !out || T <= 0 || H <= 0 || r <= 0 || dr < 0 ||
+  if (!q_abs || !proj || !ckv || !kr || !positions || !seq_of || !pages || !out || T <= 0 || H <= 0 || r <= 0 || dr < 0 ||
       window <= 0 || bad_dt(dt_cache))
     return failf(KB2SEQ_ERR_VALUE, "latent_window_attn: bad argument");
   if (r > kAttnThreads * kAttnAcc) return failf(KB2SEQ_ERR_VALUE, "latent_window_attn: latent size %d > %d", r, kAttnThreads * kAttnAcc);
@@ -1103,19 +1108,21 @@ KB2SEQ_API int kb2_seq_latent_window_attn(const float* q_abs, const float* proj,
 
 KB2SEQ_API int kb2_seq_conv(const float* proj, long long ldp, int T, int S, int C, int K, const float* taps, const float* bias, int act,
                             float* tail, const int* seq_of, const int* cu, const int* slots, float* out, void* stream) {
-  if (!proj || !taps || !tail || !seq_of || !cu || !slots || !out || T <= 0 || S <= 0 || C <= 0 || K <= 0 || act < 0 || act > 1)
+  const int bias_after = act >> 1;
+  act &= 1;
+  if (!proj || !taps || !tail || !seq_of || !cu || !slots || !out || T <= 0 || S <= 0 || C <= 0 || K <= 0 || bias_after > 1)
     return failf(KB2SEQ_ERR_VALUE, "conv: bad argument");
   if (T > 65535) return failf(KB2SEQ_ERR_VALUE, "conv: more than 65535 rows in one step");
   if (T >= 4 * kConvRun && K <= kConvMaxTaps)
     conv_run_kernel<<<dim3((C + 255) / 256, (T + kConvRun - 1) / kConvRun), 256, 0, (cudaStream_t)stream>>>(proj, ldp, C, K, taps, tail, seq_of,
-                                                                                                          cu, slots, T, out, bias, act);
+                                                                                                          cu, slots, T, out, bias, act, bias_after);
   else
     conv_silu_kernel<<<dim3((C + 255) / 256, T), 256, 0, (cudaStream_t)stream>>>(proj, ldp, C, K, taps, tail, seq_of, cu, slots, T, out, bias,
-                                                                                 act);
+                                                                                 act, bias_after);
   SEQ_LAUNCHED();
   if (K > 1) {
     const long long m = (long long)S * C;
-    conv_tail_kernel<<<(unsigned)((m + 255) / 256), 256, 0, (cudaStream_t)stream>>>(proj, ldp, C, K, tail, cu, slots, S, bias);
+    conv_tail_kernel<<<(unsigned)((m + 255) / 256), 256, 0, (cudaStream_t)stream>>>(proj, ldp, C, K, tail, cu, slots, S, bias_after ? nullptr : bias);
     SEQ_LAUNCHED();
   }
   return KB2SEQ_OK;

@@ -4,7 +4,8 @@ Each class owns its weights on the device, takes its constants as constructor ar
 libkrasis_b200_seq (`krasis_b200.seqops`): a model composes them (krasis_b200/vofelix.py).
 
   WindowLatentAttention   attention over a cached low-rank latent with one shared rotated key part, interleaved rotary positions
-                          with YaRN frequency blending, a sliding window and a per-head softmax sink
+                          with YaRN frequency blending, a sliding window and a per-head softmax sink (optional: queries through a
+                          normed latent of their own, no sink, a sigmoid output gate per element)
   GatedDeltaMixer         short causal convolutions on q / k / v, unit-norm q and k, gated delta-rule state per head in fp32
                           slots, per-head RMS norm of the read-out with a SiLU gate
   MultiMapAttention       grouped-query attention over a per-head paged cache whose heads carry several attention maps (keys per
@@ -14,7 +15,13 @@ libkrasis_b200_seq (`krasis_b200.seqops`): a model composes them (krasis_b200/vo
                           optionally another layer's cached keys and values instead of projections of its own
                           (further options: a short causal convolution on q / k / v after the projection, one RMS norm over the whole
                           of q and of k, rotation of dimension i with i + dims / 2, a frequency table of the caller, tanh soft-capped
-                          scores)
+                          scores, a softmax sink per head, mean-pooled blocks of keys and values before the window, values cached
+                          rotated by their positions with the output turned back, an output gate per element)
+  GatedLinearAttention    S <- diag(alpha) S + k v^T with one decay per key channel, alpha = sigmoid(.)^(1 / tau) from a low-rank
+                          projection; per-head RMS norm of the read-out with a SiLU gate
+  SelectiveScan           Mamba: input / gate projection, short causal convolution, input-dependent step sizes and B / C, diagonal
+                          state per channel in fp32 slots
+  SideBySide              two mixers that read the same input: each output RMS-normed over the width, then averaged
   ChannelDeltaMixer       the gated delta rule with one decay per head and key channel (low-rank decay and output-gate projections,
                           sigmoid output gate)
   GatedMLP                down(act(gate h) * (up h)): tanh-GELU, SiLU, or the clamped swish form g' sigmoid(a g') (u' + 1); without a
@@ -89,10 +96,13 @@ def yarn_table(dims: int, base: float, scaling):
 
 
 class WindowLatentAttention:
-    """weights: q [H (dn + dr), W], dkv [r + dr, W], dkv_norm [r], uk [H dn, r], uv [H dv, r], sink [H], o [W, H dv]."""
+    """weights: q [H (dn + dr), W], dkv [r + dr, W], dkv_norm [r], uk [H dn, r], uv [H dv, r], sink [H] (optional), o [W, H dv].
+    Instead of q: dq [rq, W], dq_norm [rq], uq [H (dn + dr), rq] — queries from an RMS-normed latent of their own.
+    g [H dv, W] (optional): the concatenated heads are multiplied by sigmoid(g h) ahead of the output projection.
+    rot_freq: the frequency table (fp64, one per rotated pair), if not the YaRN table of rot_base / rot_scaling."""
 
     def __init__(self, weights: dict, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float, window,
-                 rot_dims: int, rot_base: float, rot_scaling, eps: float, dtype, device):
+                 rot_dims: int, rot_base: float, rot_scaling, eps: float, dtype, device, rot_freq=None):
         self.H, self.dn, self.dr, self.dv, self.r = heads, dim, rot_dim, vdim, kv_rank
         self.scale, self.eps, self.dtype, self.device = float(scale), float(eps), dtype, device
         self.window = int(window) if window else 1 << 30
@@ -100,11 +110,24 @@ class WindowLatentAttention:
         if self.rot_dims > rot_dim or self.rot_dims % 2:
             raise ValueError("rotated dimensions must be even and at most rot_dim")
         freq, amp = yarn_table(self.rot_dims, rot_base, rot_scaling) if self.rot_dims else (torch.zeros(1, dtype=torch.float64), 1.0)
+        if rot_freq is not None:
+            freq, amp = rot_freq.to(torch.float64), 1.0
         self.freq, self.amp = freq.to(device), float(amp)
         d = lambda t: t.to(device=device, dtype=dtype).contiguous()
         f = lambda t: t.to(device=device, dtype=torch.float32).contiguous()
-        self.w_in = d(torch.cat([weights["q"], weights["dkv"]], 0))                # one projection: [q | latent | rotated key]
-        self.dkv_norm, self.sink = f(weights["dkv_norm"]), f(weights["sink"])
+        self.q_latent = "dq" in weights
+        first = weights["dq"] if self.q_latent else weights["q"]
+        self.q_cols = first.shape[0]                                               # q itself, or the query latent
+        rows = [first, weights["dkv"]]
+        self.gate_off = -1
+        if "g" in weights:
+            self.gate_off = self.q_cols + kv_rank + rot_dim
+            rows.append(weights["g"])
+        self.w_in = d(torch.cat(rows, 0))                                          # one projection: [q | latent | rotated key | gate]
+        if self.q_latent:
+            self.dq_norm, self.w_uq = f(weights["dq_norm"]), d(weights["uq"])
+        self.dkv_norm = f(weights["dkv_norm"])
+        self.sink = f(weights["sink"]) if "sink" in weights else None
         # absorbed key up-projection: q_abs[h] = q_nope[h] @ uk[h]  ->  stored [H, r, dn] for an A B^T product
         self.uk_t = d(weights["uk"].reshape(heads, dim, kv_rank).transpose(1, 2))
         self.uv = d(weights["uv"].reshape(heads, vdim, kv_rank))
@@ -120,15 +143,21 @@ class WindowLatentAttention:
 
     def forward(self, h: torch.Tensor, tb: ops.StepTables, ckv: torch.Tensor, kr: torch.Tensor, page_size: int) -> torch.Tensor:
         lib, T, H = ops.load(), h.shape[0], self.H
-        proj = lin(h, self.w_in, torch.float32)
+        proj_in = proj = lin(h, self.w_in, torch.float32)
+        lat = None
+        if self.q_latent:                         # q = uq rmsnorm(dq h); the latent and rotated key columns stay in proj_in
+            proj = lin(ops.rms_rows(proj_in[:, :self.q_cols], self.dq_norm, self.eps, self.dtype), self.w_uq, torch.float32)
+            lat = proj_in[:, self.q_cols:]
         ldp = proj.stride(0)
         s = torch.cuda.current_stream(h.device).cuda_stream
         dtc = ops.dt_code(ckv.dtype)
         ops.check(lib.kb2_seq_latent_prep(proj.data_ptr(), ldp, T, H, self.dn, self.dr, self.r, self.dkv_norm.data_ptr(), self.eps,
                                           self.freq.data_ptr(), self.rot_dims, self.amp, tb.positions.data_ptr(), tb.seq_of.data_ptr(),
-                                          tb.pages.data_ptr(), tb.max_pages, page_size, ckv.data_ptr(), kr.data_ptr(), dtc, s))
+                                          tb.pages.data_ptr(), tb.max_pages, page_size, ckv.data_ptr(), kr.data_ptr(), dtc, ops._ptr(lat),
+                                          proj_in.stride(0), s))
         q = proj[:, :H * (self.dn + self.dr)].view(T, H, self.dn + self.dr)
-        o = torch.empty((T, H, self.dv), dtype=self.dtype, device=h.device)
+        gated = self.gate_off >= 0
+        o = torch.empty((T, H, self.dv), dtype=torch.float32 if gated else self.dtype, device=h.device)
         core = _core_lib() if self.tc_shape else False
         fast = [i for i, (_, n, _, _) in enumerate(tb.layout) if n >= self.tc_min_portion] if core else []
         if len(fast) < tb.S:
@@ -143,7 +172,7 @@ class WindowLatentAttention:
             part_ml = torch.empty((T, nsplit, H, 2), dtype=torch.float32, device=h.device) if nsplit > 1 else None
             ops.check(lib.kb2_seq_latent_window_attn(q_abs.data_ptr(), proj.data_ptr(), ldp, T, H, self.dn, self.dr, self.r, ckv.data_ptr(),
                                                      kr.data_ptr(), dtc, tb.positions.data_ptr(), tb.seq_of.data_ptr(), tb.pages.data_ptr(),
-                                                     tb.max_pages, page_size, self.sink.data_ptr(), self.scale, self.window,
+                                                     tb.max_pages, page_size, ops._ptr(self.sink), self.scale, self.window,
                                                      o_lat.data_ptr(), tb.cu.data_ptr() if fast else None, self.tc_min_portion, nsplit,
                                                      part_acc.data_ptr() if nsplit > 1 else None,
                                                      part_ml.data_ptr() if nsplit > 1 else None, s))
@@ -155,9 +184,14 @@ class WindowLatentAttention:
             kv_up = lin(ckv.view(-1, self.r).index_select(0, rows), self.w_kv_up, torch.bfloat16)     # [keys, H * (128 + 128)]
             kpe = kr.view(-1, self.dr).index_select(0, rows)
             q_bf = proj[row0:row0 + n, :H * (self.dn + self.dr)].to(torch.bfloat16).contiguous()
-            capi.check(core.kb2_fmha_latent(q_bf.data_ptr(), kv_up.data_ptr(), kpe.data_ptr(), o[row0:row0 + n].data_ptr(), n, start - lo,
-                                            start - lo + n, H, self.scale, min(self.window, 1 << 30), self.sink.data_ptr(),
+            o_rows = torch.empty((n, H, self.dv), dtype=torch.bfloat16, device=h.device) if gated else o[row0:row0 + n]
+            capi.check(core.kb2_fmha_latent(q_bf.data_ptr(), kv_up.data_ptr(), kpe.data_ptr(), o_rows.data_ptr(), n, start - lo,
+                                            start - lo + n, H, self.scale, min(self.window, 1 << 30), ops._ptr(self.sink),
                                             h.device.index or 0, s))
+            if gated:
+                o[row0:row0 + n].copy_(o_rows)
+        if gated:
+            o = ops.head_norm_gate(o.view(T, H * self.dv), H, self.dv, self.dtype, gate=proj_in[:, self.gate_off:], gate_act="sigmoid")
         return lin(o.view(T, H * self.dv), self.w_o, torch.float32)
 
 
@@ -201,6 +235,106 @@ class GatedDeltaMixer:
                                          self.norm.data_ptr(), self.eps, state.data_ptr(), tb.cu.data_ptr(), tb.slots.data_ptr(),
                                          scratch.data_ptr() if scratch is not None else None, o.data_ptr(), ops.dt_code(self.dtype), s))
         return lin(o, self.w_o, torch.float32)
+
+
+def lin_cols(proj: torch.Tensor, off: int, r: int, w: torch.Tensor, dtype) -> torch.Tensor:
+    """Second factor of a low-rank projection on columns [off, off + r) of an fp32 product: fp32 out.  The generic kernel reads the
+    strided fp32 columns as they are; only a long bfloat16 step with a rank the tensor-core kernel takes is rounded and packed."""
+    a = proj[:, off:off + r]
+    if dtype == torch.bfloat16 and proj.shape[0] >= 256 and r % 64 == 0 and _core_lib():
+        return lin(a.to(torch.bfloat16).contiguous(), w, torch.float32)
+    return ops.gemm(a, w, torch.float32)
+
+
+class GatedLinearAttention:
+    """weights: q, k [H dk, W], v, g [H dv, W], a1 [r, W], a2 [H dk, r], a2_b [H dk], norm [dv], o [W, H dv].
+
+    Per token and head: alpha = sigmoid(a2 (a1 h) + a2_b)^(1 / tau), one decay per key channel; S <- diag(alpha) S + k v^T;
+    o = S^T (q dk^-1/2); out = o / rms(o) * norm * silu(g h), heads side by side, then the output projection.  The state
+    [slots, H, dk, dv], the decays and their logarithms are fp32."""
+
+    def __init__(self, weights: dict, heads: int, dim: int, vdim: int, tau: float, eps: float, dtype, device, q_scale=None):
+        self.H, self.dk, self.dv, self.tau = heads, dim, vdim, float(tau)
+        self.q_scale = float(dim) ** -0.5 if q_scale is None else float(q_scale)
+        self.eps, self.dtype, self.device = float(eps), dtype, device
+        d = lambda t: t.to(device=device, dtype=dtype).contiguous()
+        f = lambda t: t.to(device=device, dtype=torch.float32).contiguous()
+        self.ra = weights["a1"].shape[0]
+        self.q_off, self.k_off, self.v_off = 0, heads * dim, 2 * heads * dim
+        self.g_off = self.v_off + heads * vdim
+        self.a_off = self.g_off + heads * vdim
+        self.w_in = d(torch.cat([weights[k] for k in ("q", "k", "v", "g", "a1")], 0))        # one projection of the layer input
+        self.w_a2, self.a2_b, self.norm = d(weights["a2"]), f(weights["a2_b"]), f(weights["norm"])
+        if self.w_a2.shape[0] != heads * dim or self.a2_b.numel() != heads * dim or self.norm.numel() != vdim:
+            raise ValueError("decay projection / norm do not match heads x dim / vdim")
+        self.w_o = d(weights["o"])
+
+    def register_state(self, pool):
+        """Recurrent state [slots, H, dk, dv] in a RecurrentStatePool."""
+        return pool.register(self.H, self.dk, self.dv)
+
+    def forward(self, h: torch.Tensor, tb: ops.StepTables, state: torch.Tensor) -> torch.Tensor:
+        lib, T, H = ops.load(), h.shape[0], self.H
+        proj = lin(h, self.w_in, torch.float32)
+        dec_in = lin_cols(proj, self.a_off, self.ra, self.w_a2, self.dtype)                   # [T, H dk]
+        o = torch.empty((T, H * self.dv), dtype=torch.float32, device=h.device)
+        ops.check(lib.kb2_seq_gla(proj.data_ptr(), proj.stride(0), self.q_off, self.k_off, self.v_off, dec_in.data_ptr(), dec_in.stride(0),
+                                  self.a2_b.data_ptr(), self.tau, self.q_scale, T, tb.S, H, self.dk, self.dv, state.data_ptr(),
+                                  tb.cu.data_ptr(), tb.slots.data_ptr(), o.data_ptr(), torch.cuda.current_stream(h.device).cuda_stream))
+        o = ops.head_norm_gate(o, H, self.dv, self.dtype, norm=self.norm, eps=self.eps, gate=proj[:, self.g_off:], gate_act="silu")
+        return lin(o, self.w_o, torch.float32)
+
+
+class SelectiveScan:
+    """weights: in [2 C, W] (x | z), conv [C, taps], conv_b [C], x [R + 2 N, C] (dt | B | C), dt [C, R], dt_b [C], A_log [C, N], D [C],
+    o [W, C].
+
+    x = silu(causal conv(in h)[:C] + conv_b); dt = softplus(dt (x x)[:R] + dt_b) per channel; per channel c and state n:
+    S <- exp(dt_c A[c, n]) S + dt_c x_c B_n with A = -exp(A_log); y_c = sum_n S[c, n] C_n + D_c x_c; out = o (y silu(z)).
+    The state [slots, C, N], the convolution's last taps - 1 inputs, step sizes and exponentials are fp32."""
+
+    def __init__(self, weights: dict, inner: int, state: int, dt_rank: int, taps: int, dtype, device):
+        self.C, self.N, self.R, self.K = int(inner), int(state), int(dt_rank), int(taps)
+        self.dtype, self.device = dtype, device
+        d = lambda t: t.to(device=device, dtype=dtype).contiguous()
+        f = lambda t: t.to(device=device, dtype=torch.float32).contiguous()
+        self.w_in, self.w_x, self.w_dt, self.w_o = d(weights["in"]), d(weights["x"]), d(weights["dt"]), d(weights["o"])
+        self.taps, self.conv_b = f(weights["conv"]), f(weights["conv_b"])
+        self.dt_b, self.A_log, self.D = f(weights["dt_b"]), f(weights["A_log"]), f(weights["D"])
+        if (self.w_in.shape[0] != 2 * self.C or self.w_x.shape != (self.R + 2 * self.N, self.C) or self.taps.shape != (self.C, self.K)
+                or self.A_log.shape != (self.C, self.N)):
+            raise ValueError("selective scan: tensor shapes do not match inner / state / dt_rank / taps")
+
+    def register_state(self, pool):
+        """(conv tail [slots, C, taps - 1], state [slots, C, N]) in a RecurrentStatePool."""
+        return pool.register(self.C, max(self.K - 1, 1)), pool.register(self.C, self.N)
+
+    def forward(self, h: torch.Tensor, tb: ops.StepTables, tail: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
+        lib, T = ops.load(), h.shape[0]
+        proj = lin(h, self.w_in, torch.float32)                                               # [T, x: C | z: C]
+        xc = ops.conv(proj, self.C, self.taps, self.conv_b, True, tail, tb, bias_after=True)  # [T, C] fp32
+        big = self.dtype == torch.bfloat16 and T >= 256 and bool(_core_lib())
+        xp = lin(xc.to(torch.bfloat16) if big else xc, self.w_x, torch.float32, min_n=16)     # [T, dt: R | B: N | C: N]
+        dt_in = lin_cols(xp, 0, self.R, self.w_dt, self.dtype)                                # [T, C]
+        y = torch.empty((T, self.C), dtype=self.dtype, device=h.device)
+        ops.check(lib.kb2_seq_selective_scan(xc.data_ptr(), xc.stride(0), dt_in.data_ptr(), dt_in.stride(0), self.dt_b.data_ptr(),
+                                             xp.data_ptr(), xp.stride(0), self.R, proj.data_ptr(), proj.stride(0), self.C,
+                                             self.A_log.data_ptr(), self.D.data_ptr(), T, tb.S, self.C, self.N, state.data_ptr(),
+                                             tb.cu.data_ptr(), tb.slots.data_ptr(), y.data_ptr(), ops.dt_code(self.dtype),
+                                             torch.cuda.current_stream(h.device).cuda_stream))
+        return lin(y, self.w_o, torch.float32)
+
+
+class SideBySide:
+    """Two mixers read the same input; the result is coef (left / rms(left) * w_left + right / rms(right) * w_right) over the width."""
+
+    def __init__(self, left, right, w_left: torch.Tensor, w_right: torch.Tensor, eps: float, device, coef: float = 0.5):
+        self.left, self.right, self.eps, self.coef = left, right, float(eps), float(coef)
+        self.w_left = w_left.to(device=device, dtype=torch.float32).contiguous()
+        self.w_right = w_right.to(device=device, dtype=torch.float32).contiguous()
+
+    def merge(self, y_left: torch.Tensor, y_right: torch.Tensor) -> torch.Tensor:
+        return ops.branch_merge(y_left, y_right, self.w_left, self.w_right, self.eps, self.coef)
 
 
 class ChannelDeltaMixer:
@@ -322,12 +456,20 @@ class MultiMapAttention:
     projections, ahead of norm and rotation; its last taps - 1 inputs per sequence live in a state slot (`register_state`).
     norm_whole: q_norm / k_norm have the size of the whole projection and one root mean square is taken over all of q (of k).
     rot_half: dimension i turns with i + rot_dims / 2 (default: 2i with 2i + 1).  rot_freq: the frequency table, if not
-    base^(-2i / dims) / rot_factor.  softcap > 0: a scaled score s becomes softcap tanh(s / softcap)."""
+    base^(-2i / dims) / rot_factor.  softcap > 0: a scaled score s becomes softcap tanh(s / softcap).
+
+    sink [H] (optional weight): exp(sink_h) joins the softmax denominator of head h (no key, no value, not scaled).
+    pool > 0 (with a window): beside the window's keys a position sees one key and value per block of `pool` positions that lies wholly
+    before its window — the means of the block's cached keys and values, kept in pooled pools (`forward(..., pooled=(kp, vp))`).
+    rot_values: values are cached rotated by their positions over all of vdim (pair m by position * rot_base^(-2m / vdim), no factor,
+    the pair layout of the keys) and each head's output is turned back by the query's position, ahead of the gate.
+    gate_per_element: g is [H dv, W], one sigmoid gate per output element (default [H, W]: one per head)."""
 
     def __init__(self, weights: dict, heads: int, kv_heads: int, maps: int, dim: int, vdim: int, scale: float, eps: float, dtype, device,
                  chunk=None, window=None, rot_dims: int = 0, rot_base: float = 10000.0, rot_factor: float = 1.0, map_coef=None,
                  unit_norm: bool = False, post_scale: float = 1.0, own_kv: bool = True, conv_taps: int = 0, norm_whole: bool = False,
-                 rot_half: bool = False, rot_freq=None, softcap: float = 0.0):
+                 rot_half: bool = False, rot_freq=None, softcap: float = 0.0, pool: int = 0, rot_values: bool = False,
+                 gate_per_element: bool = False):
         if heads % kv_heads:
             raise ValueError("heads must be a multiple of kv_heads")
         if rot_dims > dim or rot_dims % 2:
@@ -346,8 +488,17 @@ class MultiMapAttention:
         if self.K and not own_kv:
             raise ValueError("the convolution needs projections of the layer's own")
         self.unit_norm, self.post_scale = bool(unit_norm), float(post_scale)
+        self.pool, self.gate_wide = int(pool or 0), bool(gate_per_element)
+        if self.pool and (self.chunk or not window or not own_kv):
+            raise ValueError("pooled blocks need a sliding window, no chunks and a cache of the layer's own")
+        if rot_values and vdim % 2:
+            raise ValueError("rotated values need an even value size")
+        self.vfreq = rotary_table(vdim, rot_base, 1.0).to(device) if rot_values else None
         d = lambda t: t.to(device=device, dtype=dtype).contiguous()
         f = lambda t: t.to(device=device, dtype=torch.float32).contiguous()
+        self.sink = f(weights["sink"]) if "sink" in weights else None
+        if self.sink is not None and self.sink.numel() != heads:
+            raise ValueError("one sink per head")
         self.map_coef = f(torch.as_tensor(map_coef, dtype=torch.float64)) if map_coef is not None else None
         if self.map_coef is not None and self.map_coef.numel() != self.M:
             raise ValueError("one coefficient per map")
@@ -372,10 +523,11 @@ class MultiMapAttention:
         # long prompt portions in bfloat16 with 128 query / key dims per map and 128 or 256 value dims run the tcgen05 attention core of
         # the MoE prefill models, one call per chunk the portion touches, on keys and values gathered from the pages
         self.tc_min_portion = 128
-        self.tc_shape = dtype == torch.bfloat16 and dim == 128 and vdim in (128, 256)
+        self.tc_shape = dtype == torch.bfloat16 and dim == 128 and vdim in (128, 256) and self.sink is None and not self.pool
 
     def cache_dims(self):
-        return self.G * self.M * self.d, self.G * self.dv
+        """(key width, value width) of a cache row; with pooled blocks a third entry, the block length."""
+        return (self.G * self.M * self.d, self.G * self.dv) + ((self.pool,) if self.pool else ())
 
     def register_state(self, pool):
         """Convolution tail [slots, C, taps - 1] in a RecurrentStatePool (None without a convolution)."""
@@ -409,8 +561,11 @@ class MultiMapAttention:
                                                   self.softcap, min(self.window, 1 << 30), proj.device.index or 0, stream))
             pos = end
 
-    def forward(self, h: torch.Tensor, tb: ops.StepTables, kc: torch.Tensor, vc: torch.Tensor, page_size: int, tail=None) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, tb: ops.StepTables, kc: torch.Tensor, vc: torch.Tensor, page_size: int, tail=None, pooled=None) -> torch.Tensor:
         lib, T, H, G, M = ops.load(), h.shape[0], self.H, self.G, self.M
+        if self.pool and pooled is None:
+            raise ValueError("this layer needs its pooled pools")
+        kp, vp = pooled if self.pool else (None, None)
         proj_in = proj = lin(h, self.w_in, torch.float32)
         bias = self.bias
         if self.K:                                   # q | k | v through the convolution (bias first); the gate columns stay in proj_in
@@ -421,10 +576,13 @@ class MultiMapAttention:
         ops.check(lib.kb2_seq_head_kv_prep(proj.data_ptr(), ldp, T, H, G if self.own_kv else 0, M, self.d, self.dv, ops._ptr(bias),
                                            ops._ptr(self.q_norm), ops._ptr(self.k_norm), self.eps, ops._ptr(self.freq), self.rot_dims,
                                            tb.positions.data_ptr(), tb.seq_of.data_ptr(), tb.pages.data_ptr(), tb.max_pages, page_size,
-                                           kc.data_ptr(), vc.data_ptr(), dtc, int(self.norm_whole), int(self.rot_half), s))
+                                           kc.data_ptr(), vc.data_ptr(), dtc, int(self.norm_whole), int(self.rot_half), ops._ptr(self.vfreq), s))
+        if self.pool:                                # the tokens that complete a block write its mean key and value
+            ops.check(lib.kb2_seq_kv_pool(kc.data_ptr(), vc.data_ptr(), kp.data_ptr(), vp.data_ptr(), dtc, G * M * self.d, G * self.dv, self.pool,
+                                          T, tb.positions.data_ptr(), tb.seq_of.data_ptr(), tb.pages.data_ptr(), tb.max_pages, page_size, s))
         # a step of few tokens (decoding) cuts each token's keys into pieces so that the whole GPU works on them
         reach = min(self.window, self.chunk) if self.chunk else self.window
-        max_keys = max(min(reach, start + n) for _, n, start, _ in tb.layout)
+        max_keys = max(min(reach, start + n) + ((start + n) // self.pool if self.pool else 0) for _, n, start, _ in tb.layout)
         nsplit = max(1, min(296 // max(T * G, 1), (max_keys + 31) // 32, 64))
         core = _core_lib() if self.tc_shape else False
         fast = [i for i, (_, n, _, _) in enumerate(tb.layout) if n >= self.tc_min_portion] if core else []
@@ -441,14 +599,16 @@ class MultiMapAttention:
             ops.check(lib.kb2_seq_paged_attn(proj.data_ptr(), ldp, T, H, G, M, self.d, self.dv, kc.data_ptr(), vc.data_ptr(), dtc,
                                              tb.positions.data_ptr(), tb.seq_of.data_ptr(), tb.pages.data_ptr(), tb.max_pages, page_size,
                                              self.scale, self.chunk, min(self.window, 1 << 30), a.data_ptr(), nsplit, ops._ptr(part_acc),
-                                             ops._ptr(part_ml), tb.cu.data_ptr() if fast else None, self.tc_min_portion, self.softcap, s))
+                                             ops._ptr(part_ml), tb.cu.data_ptr() if fast else None, self.tc_min_portion, self.softcap,
+                                             ops._ptr(self.sink), self.pool, ops._ptr(kp), ops._ptr(vp), s))
         for i in fast:
             self._tensor_core_portion(core, proj, a, tb, i, kc, vc, page_size, s)
         o = torch.empty((T, H * self.dv), dtype=self.dtype, device=h.device)
         gate = proj_in[:, self.gate_off:] if self.gate_off >= 0 else None
         ops.check(lib.kb2_seq_attn_finish(a.data_ptr(), ops._ptr(part_acc), ops._ptr(part_ml), nsplit, T, H, M, self.dv, ops._ptr(self.map_coef),
                                           int(self.unit_norm), self.eps, self.post_scale, ops._ptr(gate), proj_in.stride(0), o.data_ptr(),
-                                          ops.dt_code(self.dtype), None, None, 0, s))
+                                          ops.dt_code(self.dtype), None, None, 0, int(self.gate_wide), tb.positions.data_ptr(),
+                                          ops._ptr(self.vfreq), int(self.rot_half), s))
         return lin(o, self.w_o, torch.float32)
 
 

@@ -38,6 +38,13 @@ def _gurozen(model_dir, dtype=torch.bfloat16, device=0, **kw):
     return GurozenModel.from_pretrained(model_dir, dtype=dtype, device=device, **kw)
 
 
+def _zaronex(model_dir, dtype=torch.bfloat16, device=0, **kw):
+    from .build import build_seq
+    build_seq()
+    from .zaronex import ZaronexModel
+    return ZaronexModel.from_pretrained(model_dir, dtype=dtype, device=device, **kw)
+
+
 def _hf_moe(model_dir, dtype=torch.bfloat16, device=0, **kw):
     if dtype != torch.bfloat16:
         raise ValueError("the MoE prefill models run in bfloat16 only")
@@ -50,6 +57,7 @@ def _hf_moe(model_dir, dtype=torch.bfloat16, device=0, **kw):
 register("Vofelix", _vofelix)
 register("Megolorn", _megolorn)
 register("Gurozen", _gurozen)
+register("Zaronex", _zaronex)
 for _name in _HF_MOE:
     register(_name, _hf_moe)
 

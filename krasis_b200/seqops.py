@@ -21,7 +21,7 @@ SIGNATURES = {
     "kb2_seq_residual_norm": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
     "kb2_seq_act_mul": (_I, [_P, _I, _P, _I, _I, _I, _P]),
     "kb2_seq_side_gate": (_I, [_P, _P, _I, _L, _P, _I, _I, _I, _P, _I, _P]),
-    "kb2_seq_latent_prep": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _F, _P, _I, _F, _P, _P, _P, _I, _I, _P, _P, _I, _P]),
+    "kb2_seq_latent_prep": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _F, _P, _I, _F, _P, _P, _P, _I, _I, _P, _P, _I, _P, _L, _P]),
     "kb2_seq_latent_window_attn": (_I, [_P, _P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _F, _I, _P, _P, _I, _I, _P, _P, _P]),
     "kb2_seq_conv_silu": (_I, [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
     "kb2_seq_delta_rule": (_I, [_P, _I, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P, _P, _P, _I, _P]),
@@ -29,9 +29,11 @@ SIGNATURES = {
     "kb2_seq_residual_scale_rms": (_I, [_P, _P, _F, _P, _F, _P, _I, _I, _I, _F, _P]),
     "kb2_seq_delta_rule_ch": (_I, [_P, _I, _P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P, _P, _P, _I, _P]),
     "kb2_seq_residual_add_norm": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
-    "kb2_seq_head_kv_prep": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _P]),
-    "kb2_seq_paged_attn": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _F, _I, _I, _P, _I, _P, _P, _P, _I, _F, _P]),
-    "kb2_seq_attn_finish": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _F, _F, _P, _L, _P, _I, _P, _P, _I, _P]),
+    "kb2_seq_head_kv_prep": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _P, _P]),
+    "kb2_seq_kv_pool": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P]),
+    "kb2_seq_paged_attn": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _F, _I, _I, _P, _I, _P, _P, _P, _I, _F, _P, _I,
+                                _P, _P, _P]),
+    "kb2_seq_attn_finish": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _F, _F, _P, _L, _P, _I, _P, _P, _I, _I, _P, _P, _I, _P]),
     "kb2_seq_glu": (_I, [_P, _I, _L, _P, _I, _L, _I, _I, _F, _F, _P, _I, _P]),
     "kb2_seq_route": (_I, [_P, _L, _I, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P]),
     "kb2_seq_moe_tile_rows": (_I, []),
@@ -39,6 +41,12 @@ SIGNATURES = {
     "kb2_seq_moe_gemm": (_I, [_P, _I, _L, _P, _I, _P, _I, _L, _L, _P, _I, _L, _I, _I, _P, _P, _I, _I, _P]),
     "kb2_seq_moe_gemv": (_I, [_P, _I, _L, _I, _P, _I, _P, _I, _L, _L, _P, _I, _L, _I, _I, _I, _P]),
     "kb2_seq_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _P, _P, _I, _P, _L, _P]),
+    "kb2_seq_gla": (_I, [_P, _L, _I, _I, _I, _P, _L, _P, _F, _F, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "kb2_seq_selective_scan": (_I, [_P, _L, _P, _L, _P, _P, _L, _I, _P, _L, _I, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _I, _P]),
+    "kb2_seq_head_norm_gate": (_I, [_P, _L, _P, _F, _P, _L, _I, _I, _I, _I, _P, _I, _P]),
+    "kb2_seq_rms_rows": (_I, [_P, _L, _I, _P, _F, _P, _I, _L, _I, _P]),
+    "kb2_seq_branch_merge": (_I, [_P, _P, _P, _P, _F, _F, _P, _I, _I, _P]),
+    "kb2_seq_depth_mix": (_I, [_P, _L, _I, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
 }
 
 _lib = None
@@ -268,12 +276,13 @@ def residual_scale_rms(x, y=None, y_mult: float = 1.0, norm=None, w_shift: float
     return h
 
 
-def conv(proj: torch.Tensor, C: int, taps: torch.Tensor, bias, act: bool, tail: torch.Tensor, tb: "StepTables") -> torch.Tensor:
+def conv(proj: torch.Tensor, C: int, taps: torch.Tensor, bias, act: bool, tail: torch.Tensor, tb: "StepTables", bias_after: bool = False) -> torch.Tensor:
     """Short causal convolution over time on the first C columns of proj [T, >= C] fp32 (+ bias), with the carried tail
-    [slots, C, taps - 1] read and advanced; silu on the result if act."""
+    [slots, C, taps - 1] read and advanced; silu on the result if act.  bias_after: the bias is added to the convolution's result
+    (ahead of the activation) instead of to its inputs."""
     T, K = proj.shape[0], taps.shape[1]
     out = torch.empty((T, C), dtype=torch.float32, device=proj.device)
-    check(load().kb2_seq_conv(proj.data_ptr(), proj.stride(0), T, tb.S, C, K, taps.data_ptr(), _ptr(bias), int(bool(act)), tail.data_ptr(),
+    check(load().kb2_seq_conv(proj.data_ptr(), proj.stride(0), T, tb.S, C, K, taps.data_ptr(), _ptr(bias), int(bool(act)) + 2 * int(bool(bias_after)), tail.data_ptr(),
                               tb.seq_of.data_ptr(), tb.cu.data_ptr(), tb.slots.data_ptr(), out.data_ptr(), _s(proj)))
     return out
 
@@ -292,3 +301,47 @@ def route(z: torch.Tensor, correction, top: int, groups: int = 1, keep: int = 1,
                                int(top), int(renorm), float(out_scale), ids.data_ptr(), w.data_ptr(), {"max": 0, "top2": 1}[group_score],
                                _s(z)))
     return ids, w
+
+
+def rms_rows(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype) -> torch.Tensor:
+    """x [T, n] fp32 rows (row stride free) -> x / rms(x) * w, contiguous in out_dtype."""
+    T, n = x.shape
+    if x.dtype != torch.float32 or x.stride(1) != 1:
+        raise ValueError("rms_rows: fp32 rows")
+    out = torch.empty((T, n), dtype=out_dtype, device=x.device)
+    check(load().kb2_seq_rms_rows(x.data_ptr(), x.stride(0), n, w.data_ptr(), float(eps), out.data_ptr(), dt_code(out_dtype), n, T, _s(x)))
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, H: int, dv: int, out_dtype, norm=None, eps: float = 0.0, gate=None, gate_act: str = "silu") -> torch.Tensor:
+    """o [T, >= H dv] fp32 -> per head o / rms(o) * norm (if norm) times silu | sigmoid of gate [T, >= H dv] (if gate), in out_dtype."""
+    T = o.shape[0]
+    out = torch.empty((T, H * dv), dtype=out_dtype, device=o.device)
+    check(load().kb2_seq_head_norm_gate(o.data_ptr(), o.stride(0), _ptr(norm), float(eps), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                        {"silu": 0, "sigmoid": 1}[gate_act], T, H, dv, out.data_ptr(), dt_code(out_dtype), _s(o)))
+    return out
+
+
+def branch_merge(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float, coef: float = 0.5) -> torch.Tensor:
+    """coef (a / rms(a) * wa + b / rms(b) * wb) per row; a, b contiguous fp32 [T, W]."""
+    for t in (a, b):
+        if t.dtype != torch.float32 or not t.is_contiguous() or t.shape != a.shape:
+            raise ValueError("branch_merge: contiguous fp32 rows of one shape")
+    out = torch.empty_like(a)
+    check(load().kb2_seq_branch_merge(a.data_ptr(), b.data_ptr(), wa.data_ptr(), wb.data_ptr(), float(eps), float(coef), out.data_ptr(),
+                                      a.shape[0], a.shape[1], _s(a)))
+    return out
+
+
+def depth_mix(stack: torch.Tensor, n: int, coef: torch.Tensor, x: torch.Tensor, y=None, norm=None, out_dtype=torch.float32, eps: float = 1e-5):
+    """stack [>= n, T, W] fp32 holds n - 1 earlier results; entry n - 1 <- x + y; x <- sum_j coef[j] stack[j]; returns
+    x / rms(x) * norm in out_dtype (None without `norm`)."""
+    T, W = x.shape
+    if stack.dtype != torch.float32 or not stack.is_contiguous() or stack.shape[0] < n or stack.shape[1:] != x.shape or coef.numel() < n:
+        raise ValueError("depth_mix: stack [>= n, T, W] fp32 and n coefficients")
+    if x.dtype != torch.float32 or not x.is_contiguous() or (y is not None and (y.dtype != torch.float32 or not y.is_contiguous())):
+        raise ValueError("depth_mix: x and y must be contiguous fp32")
+    h = torch.empty((T, W), dtype=out_dtype, device=x.device) if norm is not None else None
+    check(load().kb2_seq_depth_mix(stack.data_ptr(), stack.stride(0), n, coef.data_ptr(), x.data_ptr(), _ptr(y), _ptr(norm), _ptr(h),
+                                   dt_code(out_dtype) if h is not None else 0, T, W, float(eps), _s(x)))
+    return h
