@@ -486,11 +486,13 @@ def main():
     ap.add_argument("--cpu-format", default="int4", choices=["int4", "gguf"],
                     help="CPU arm: int4 = moe_forward_unified on INT4 g128 (default); gguf = moe_forward_gguf on native Q4_K/Q8_0 blocks "
                          "(BASELINE configs[0]: --config v2lite --impl reference --cpu-format gguf --tokens 2048)")
-    ap.add_argument("--arch", default="moe", choices=["moe", "vofelix", "megolorn", "gurozen"],
+    ap.add_argument("--arch", default="moe", choices=["moe", "vofelix", "megolorn", "gurozen", "zaronex"],
                     help="moe (default): the BASELINE workload above; vofelix: prefill / decode throughput of the ragged-batch model at "
                          "real layer sizes beside the Gated-DeltaNet and MLA blocks at equal size (1 GPU); megolorn: the same for the "
                          "differential-attention / routed-expert model beside Vofelix and the GQA block at equal size; gurozen: the same for "
-                         "the capped-attention / channel-decay delta rule / squared-relu expert model beside the Megolorn and Vofelix blocks")
+                         "the capped-attention / channel-decay delta rule / squared-relu expert model beside the Megolorn and Vofelix blocks; "
+                         "zaronex: the same for the depth-averaged model of side-by-side mixers (pooled-block attention, gated linear "
+                         "attention, selective scan, latent attention) beside the Gurozen and Vofelix blocks, with its new kernels alone")
     args = ap.parse_args()
     if args.arch == "vofelix":
         from krasis_b200.bench_seq import run as run_seq
@@ -503,6 +505,10 @@ def main():
     if args.arch == "gurozen":
         from krasis_b200.bench_seq import run_gurozen
         run_gurozen(args, peaks())
+        return
+    if args.arch == "zaronex":
+        from krasis_b200.bench_seq import run_zaronex
+        run_zaronex(args, peaks())
         return
     args.tokens = args.tokens or DEFAULT_TOKENS[args.config]
     if args.impl == "reference":

@@ -188,10 +188,12 @@ KB2SEQ_API int kb2_seq_moe_combine(const float* y, const int* pos_of_slot, const
 /* Gated linear attention over each sequence's portion: per head S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T q_t with
  * alpha_t[i] = sigmoid(decay_in[t, h dk + i] + decay_bias[h dk + i])^(1 / tau) (decay_bias may be null).  qkv [T, ld] fp32 holds q and k
  * (H x dk columns from q_off / k_off; q is multiplied by q_scale) and v (H x dv from v_off).  state [slots][H][dk][dv] fp32 is read and
- * written back; out [T, H dv] fp32 is the raw read-out (kb2_seq_head_norm_gate finishes it). */
+ * written back; out [T, H dv] fp32 is the raw read-out (kb2_seq_head_norm_gate finishes it).
+ * scratch (fp32, T H dk elements, 16-byte aligned; may be null) selects the register-state kernel when dk is 32, 64, 128 or 256, dv a
+ * multiple of 32, and qkv, ld and the three offsets are multiples of 16 bytes; otherwise a generic kernel runs (any dk <= 1024, any dv). */
 KB2SEQ_API int kb2_seq_gla(const float* qkv, long long ld, int q_off, int k_off, int v_off, const float* decay_in, long long lda,
                            const float* decay_bias, float tau, float q_scale, int T, int S, int H, int dk, int dv, float* state,
-                           const int* cu, const int* slots, float* out, void* stream);
+                           const int* cu, const int* slots, float* scratch, float* out, void* stream);
 
 /* Selective scan over each sequence's portion: per channel c and state n, S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n,
  * y_c = sum_n S[c, n] C_n + D[c] x_c, out = y_c silu(z_c), with dt = softplus(dt_in + dt_bias), A = -exp(A_log [inner, N]).

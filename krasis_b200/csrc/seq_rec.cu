@@ -1,11 +1,12 @@
 // Ragged-batch sequence operators, third part: linear recurrences with per-sequence state slots and the small row kernels of
 // designs that run several mixers side by side or average their residual stream over depth.
 //
-//   gla_scan               gated linear attention, S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T q_t per head, with one decay per key
+//   gla_scan / gla_reg     gated linear attention, S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T q_t per head, with one decay per key
 //                          channel alpha = sigmoid(z)^(1 / tau); the state of a (sequence, head, slice of value columns) lives in
-//                          registers, P lanes share a column and each keeps dk / P of its rows
+//                          registers: a generic form (P lanes share a column and each keeps dk / P of its rows) and, for key sizes
+//                          32 / 64 / 128 / 256, a form with lane = column, warp = slice of rows and cp.async token tiles
 //   selective_scan         S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n, y_c = sum_n S[c, n] C_n + D_c x_c, times silu(z);
-//                          the lanes of a channel keep its states in registers
+//                          the lanes of a channel keep its states in registers; their pieces of y meet in shared memory once per tile
 //   head_norm_gate         per head: o / rms(o) * w (optional) times silu or sigmoid of a gate column (optional)
 //   rms_rows               RMS norm of a column range of strided fp32 rows
 //   branch_merge           c (a / rms(a) * wa + b / rms(b) * wb): two mixers that read the same input, each normed, averaged
@@ -90,10 +91,118 @@ __global__ void __launch_bounds__(kRecThreads) gla_scan_kernel(const float* __re
   }
 }
 
+// The same recurrence for key sizes 32, 64, 128 and 256 with value sizes that are multiples of 32 (the sizes of real models): a block
+// owns 32 value columns of a (sequence, head); lane = column, so that the state moves in whole 128-byte rows; warp w keeps rows
+// [w DK / 8, (w + 1) DK / 8) of its column in registers.  A token's alpha, k and q values are the same address for every lane (one
+// shared-memory transaction per 16 bytes); tiles of kGlaTile tokens arrive by cp.async, double-buffered, from the projection itself and
+// from the decays that gla_decay_kernel wrote; the warps' pieces of S^T q meet in shared memory once per tile.  No barrier inside a token.
+__global__ void gla_decay_kernel(const float* __restrict__ decay_in, long long lda, const float* __restrict__ decay_bias, float inv_tau,
+                                 long long T, int n, float* __restrict__ alpha) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * n) return;
+  const long long t = i / n;
+  const int c = (int)(i - t * n);
+  const float z = decay_in[t * lda + c] + (decay_bias ? decay_bias[c] : 0.f);
+  alpha[i] = expf(-softplus_f(-z) * inv_tau);
+}
+
+__device__ __forceinline__ void rec_cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void rec_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void rec_cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+constexpr int kGlaTile = 8, kGlaWarps = 8;
+template <int DK>
+__global__ void __launch_bounds__(32 * kGlaWarps) gla_reg_kernel(const float* __restrict__ qkv, long long ld, int q_off, int k_off, int v_off,
+                                                                 const float* __restrict__ alpha, float q_scale, int H, int dv,
+                                                                 float* __restrict__ state, const int* __restrict__ cu,
+                                                                 const int* __restrict__ slots, float* __restrict__ out) {
+  constexpr int P = kGlaWarps, NT = 32 * P, Q = DK / P;
+  extern __shared__ __align__(16) float sm[];
+  float* as = sm;                                   // [2][kGlaTile][DK]
+  float* ks = as + 2 * kGlaTile * DK;
+  float* qs = ks + 2 * kGlaTile * DK;
+  float* vs = qs + 2 * kGlaTile * DK;               // [2][kGlaTile][32]
+  float* os_part = vs + 2 * kGlaTile * 32;          // [kGlaTile][P][32]
+  const int s = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * 32;
+  const int tid = threadIdx.x, lane = tid & 31, piece = tid >> 5;
+  const int t0 = cu[s], n = cu[s + 1] - cu[s];
+  float* Sg = state + ((long long)slots[s] * H + h) * DK * dv;
+  float S[Q];
+#pragma unroll
+  for (int ii = 0; ii < Q; ++ii) S[ii] = Sg[(long long)(piece * Q + ii) * dv + j0 + lane];
+
+  auto load_tile = [&](int buf, int b0) {
+    const int nt = min(kGlaTile, n - b0);
+    for (int c = tid; c < nt * (DK / 4); c += NT) {                  // 16-byte chunks of the alpha, k and q rows
+      const int tt = c / (DK / 4), cc = c - tt * (DK / 4);
+      const long long row = t0 + b0 + tt;
+      const int dst = (buf * kGlaTile + tt) * DK + cc * 4;
+      rec_cp_async16(as + dst, alpha + (row * H + h) * DK + cc * 4);
+      rec_cp_async16(ks + dst, qkv + row * ld + k_off + h * DK + cc * 4);
+      rec_cp_async16(qs + dst, qkv + row * ld + q_off + h * DK + cc * 4);
+    }
+    for (int c = tid; c < nt * 8; c += NT) {
+      const int tt = c >> 3, cc = c & 7;
+      rec_cp_async16(vs + (buf * kGlaTile + tt) * 32 + cc * 4, qkv + (long long)(t0 + b0 + tt) * ld + v_off + h * dv + j0 + cc * 4);
+    }
+    rec_cp_async_commit();
+  };
+
+  load_tile(0, 0);
+  int buf = 0;
+  for (int b0 = 0; b0 < n; b0 += kGlaTile, buf ^= 1) {
+    const int nt = min(kGlaTile, n - b0);
+    rec_cp_async_wait_all();
+    __syncthreads();                                  // tile `buf` is in place; everyone is done with the other buffer and with os_part
+    if (b0 + kGlaTile < n) load_tile(buf ^ 1, b0 + kGlaTile);
+    for (int tt = 0; tt < nt; ++tt) {
+      const int base = (buf * kGlaTile + tt) * DK + piece * Q;
+      const float4* a4 = reinterpret_cast<const float4*>(as + base);
+      const float4* k4 = reinterpret_cast<const float4*>(ks + base);
+      const float4* q4 = reinterpret_cast<const float4*>(qs + base);
+      const float vv = vs[(buf * kGlaTile + tt) * 32 + lane];
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+      for (int ii = 0; ii < Q / 4; ++ii) {
+        const float4 ar = a4[ii], kr = k4[ii], qr = q4[ii];
+        S[4 * ii] = fmaf(S[4 * ii], ar.x, kr.x * vv);
+        S[4 * ii + 1] = fmaf(S[4 * ii + 1], ar.y, kr.y * vv);
+        S[4 * ii + 2] = fmaf(S[4 * ii + 2], ar.z, kr.z * vv);
+        S[4 * ii + 3] = fmaf(S[4 * ii + 3], ar.w, kr.w * vv);
+        a0 = fmaf(S[4 * ii], qr.x, a0);
+        a1 = fmaf(S[4 * ii + 1], qr.y, a1);
+        a2 = fmaf(S[4 * ii + 2], qr.z, a2);
+        a3 = fmaf(S[4 * ii + 3], qr.w, a3);
+      }
+      os_part[(tt * P + piece) * 32 + lane] = (a0 + a1) + (a2 + a3);
+    }
+    __syncthreads();
+    for (int i = tid; i < nt * 32; i += NT) {
+      const int tt = i >> 5, c = i & 31;
+      float o = 0.f;
+#pragma unroll
+      for (int p = 0; p < P; ++p) o += os_part[(tt * P + p) * 32 + c];
+      out[((long long)(t0 + b0 + tt) * H + h) * dv + j0 + c] = o * q_scale;
+    }
+  }
+#pragma unroll
+  for (int ii = 0; ii < Q; ++ii) Sg[(long long)(piece * Q + ii) * dv + j0 + lane] = S[ii];
+}
+
 // ------------------------------------------------------------------------------------------------ selective scan
 // x [T, ldx] (inner channels after convolution and activation), dt_in [T, ldd] (+ dt_bias, then softplus), bc [T, ldb] = [B: N | C: N]
 // from b_off, z [T, ldz] from z_off, A_log [inner, N], D [inner].  Block (sequence, group of CB channels); lane l: state slice
 // p = l % P, channel l / P of the warp; thread states are n = p + P ii, ii < NR.
+__device__ __forceinline__ void rec_cp_async4(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+
+// Tiles of kRecTok tokens arrive by cp.async, double-buffered (dt input, x, z of the block's channels; B and C of the token), so that
+// the loads of the next tile run under the recurrence of this one.  Per tile: step sizes (softplus) once per (token, channel); the
+// recurrence with nothing but shared memory and registers inside and no exchange between lanes; then the lanes' pieces of y are summed,
+// D x added, the gate applied and the rows written.
 template <int NR>
 __global__ void __launch_bounds__(kRecThreads) selective_scan_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ dt_in,
                                                                      long long ldd, const float* __restrict__ dt_bias,
@@ -104,11 +213,14 @@ __global__ void __launch_bounds__(kRecThreads) selective_scan_kernel(const float
                                                                      const int* __restrict__ slots, void* __restrict__ out, int dt_out) {
   extern __shared__ __align__(16) float sm[];
   const int CW = 32 / P, CB = (kRecThreads / 32) * CW;
-  float2* bcs = reinterpret_cast<float2*>(sm);              // [kRecTok][N]: (B_n, C_n)
-  float2* dx = reinterpret_cast<float2*>(sm + 2 * kRecTok * N);   // [kRecTok][CB]: (dt_c, x_c)
+  float* bcs = sm;                                   // [2][kRecTok][2 N]: B | C of the token
+  float* dts = bcs + 2 * kRecTok * 2 * N;            // [2][kRecTok][CB]: dt input, then the step size
+  float* xs = dts + 2 * kRecTok * CB;                // [2][kRecTok][CB]
+  float* zs = xs + 2 * kRecTok * CB;                 // [2][kRecTok][CB]
+  float* yp = zs + 2 * kRecTok * CB;                 // [kRecTok][threads]: every lane's piece of y, summed once per tile
   const int s = blockIdx.x, c0 = blockIdx.y * CB;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int p = lane % P, cl = warp * CW + lane / P, c = c0 + cl;
+  const int p = lane % P, cl = warp * CW + lane / P, c = c0 + cl;   // tid == cl * P + p
   const bool live = c < inner;
   const int row0 = cu[s], n = cu[s + 1] - row0;
   float* S = state + (long long)slots[s] * inner * N;
@@ -118,48 +230,67 @@ __global__ void __launch_bounds__(kRecThreads) selective_scan_kernel(const float
     const int j = p + P * ii;
     const bool ok = live && j < N;
     st[ii] = ok ? S[(long long)c * N + j] : 0.f;
-    a[ii] = ok ? -expf(A_log[(long long)c * N + j]) : 0.f;
+    a[ii] = ok ? -expf(A_log[(long long)c * N + j]) * 1.4426950408889634f : 0.f;      // A log2(e): exp(dt A) = 2^(dt a)
   }
-  const float dw = live ? Dw[c] : 0.f;
-  for (int t0 = 0; t0 < n; t0 += kRecTok) {
+  const int ncb = min(CB, inner - c0);               // channels of this block that exist
+
+  auto load_tile = [&](int buf, int b0) {
+    const int nt = min(kRecTok, n - b0);
+    for (int e = tid; e < nt * 2 * N; e += kRecThreads) {
+      const int tt = e / (2 * N), j = e - tt * 2 * N;
+      rec_cp_async4(bcs + (buf * kRecTok + tt) * 2 * N + j, bc + (long long)(row0 + b0 + tt) * ldb + b_off + j);
+    }
+    for (int e = tid; e < nt * ncb; e += kRecThreads) {
+      const int tt = e / ncb, cc = e - tt * ncb;
+      const long long t = row0 + b0 + tt;
+      const int dst = (buf * kRecTok + tt) * CB + cc;
+      rec_cp_async4(dts + dst, dt_in + t * ldd + c0 + cc);
+      rec_cp_async4(xs + dst, x + t * ldx + c0 + cc);
+      rec_cp_async4(zs + dst, z + t * ldz + z_off + c0 + cc);
+    }
+    rec_cp_async_commit();
+  };
+
+  load_tile(0, 0);
+  int buf = 0;
+  for (int t0 = 0; t0 < n; t0 += kRecTok, buf ^= 1) {
     const int nt = min(kRecTok, n - t0);
-    __syncthreads();
-    for (int e = tid; e < nt * N; e += kRecThreads) {
-      const int tt = e / N, j = e - tt * N;
-      const float* r = bc + (long long)(row0 + t0 + tt) * ldb + b_off;
-      bcs[e] = make_float2(r[j], r[N + j]);
-    }
-    for (int e = tid; e < nt * CB; e += kRecThreads) {
-      const int tt = e / CB, cc = e - tt * CB;
-      const long long t = row0 + t0 + tt;
-      float2 f = make_float2(0.f, 0.f);
-      if (c0 + cc < inner) {
-        f.x = softplus_f(dt_in[t * ldd + c0 + cc] + dt_bias[c0 + cc]);
-        f.y = x[t * ldx + c0 + cc];
-      }
-      dx[e] = f;
+    rec_cp_async_wait_all();
+    __syncthreads();                                 // tile `buf` is in place; everyone is done with the other buffer and with yp
+    if (t0 + kRecTok < n) load_tile(buf ^ 1, t0 + kRecTok);
+    for (int e = tid; e < nt * ncb; e += kRecThreads) {
+      const int tt = e / ncb, cc = e - tt * ncb;
+      float* d = dts + (buf * kRecTok + tt) * CB + cc;
+      *d = softplus_f(*d + dt_bias[c0 + cc]);
     }
     __syncthreads();
-    for (int tt = 0; tt < nt; ++tt) {
-      const float2 f = dx[tt * CB + cl];
-      const float dtx = f.x * f.y;
-      const float2* row = bcs + tt * N;
-      float y = 0.f;
+    if (live) {
+#pragma unroll 4
+      for (int tt = 0; tt < nt; ++tt) {
+        const float dtv = dts[(buf * kRecTok + tt) * CB + cl];
+        const float dtx = dtv * xs[(buf * kRecTok + tt) * CB + cl];
+        const float* row = bcs + (buf * kRecTok + tt) * 2 * N;
+        float y = 0.f;
 #pragma unroll
-      for (int ii = 0; ii < NR; ++ii) {
-        const int j = p + P * ii;
-        if (j < N) {
-          const float2 g = row[j];
-          st[ii] = fmaf(expf(f.x * a[ii]), st[ii], dtx * g.x);
-          y = fmaf(st[ii], g.y, y);
+        for (int ii = 0; ii < NR; ++ii) {
+          const int j = p + P * ii;
+          if (j < N) {
+            st[ii] = fmaf(exp2f(dtv * a[ii]), st[ii], dtx * row[j]);
+            y = fmaf(st[ii], row[N + j], y);
+          }
         }
+        yp[tt * kRecThreads + tid] = y;
       }
-      for (int off = 1; off < P; off <<= 1) y += __shfl_xor_sync(0xffffffffu, y, off);
-      if (p == 0 && live) {
-        const long long t = row0 + t0 + tt;
-        y = fmaf(dw, f.y, y);
-        st_dt(out, dt_out, t * inner + c, y * silu(z[t * ldz + z_off + c]));
-      }
+    }
+    __syncthreads();
+    for (int e = tid; e < nt * ncb; e += kRecThreads) {
+      const int tt = e / ncb, cc = e - tt * ncb;
+      const float* pieces = yp + tt * kRecThreads + cc * P;
+      float y = 0.f;
+      for (int q = 0; q < P; ++q) y += pieces[q];
+      const int src = (buf * kRecTok + tt) * CB + cc;
+      y = fmaf(Dw[c0 + cc], xs[src], y);
+      st_dt(out, dt_out, (long long)(row0 + t0 + tt) * inner + c0 + cc, y * silu(zs[src]));
     }
   }
 #pragma unroll
@@ -259,6 +390,16 @@ static int pow2_at_least(int v) {
   return p;
 }
 
+template <int DK>
+static int launch_gla_reg(const float* qkv, long long ld, int q_off, int k_off, int v_off, const float* alpha, float q_scale, int S, int H,
+                          int dv, float* state, const int* cu, const int* slots, float* out, cudaStream_t st) {
+  const size_t smem = (size_t)(3 * 2 * kGlaTile * DK + 2 * kGlaTile * 32 + kGlaTile * kGlaWarps * 32) * 4;
+  if (smem > 48 * 1024) SEQ_CUDA(cudaFuncSetAttribute(gla_reg_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  gla_reg_kernel<DK><<<dim3(S, H, dv / 32), 32 * kGlaWarps, smem, st>>>(qkv, ld, q_off, k_off, v_off, alpha, q_scale, H, dv, state, cu, slots, out);
+  SEQ_LAUNCHED();
+  return KB2SEQ_OK;
+}
+
 }  // namespace kb2seq
 
 using namespace kb2seq;
@@ -267,11 +408,23 @@ extern "C" {
 
 KB2SEQ_API int kb2_seq_gla(const float* qkv, long long ld, int q_off, int k_off, int v_off, const float* decay_in, long long lda,
                            const float* decay_bias, float tau, float q_scale, int T, int S, int H, int dk, int dv, float* state,
-                           const int* cu, const int* slots, float* out, void* stream) {
+                           const int* cu, const int* slots, float* scratch, float* out, void* stream) {
   if (!qkv || !decay_in || !state || !cu || !slots || !out || T <= 0 || S <= 0 || H <= 0 || dk <= 0 || dv <= 0 || !(tau > 0.f))
     return failf(KB2SEQ_ERR_VALUE, "gla: bad argument");
   if (dk > 1024) return failf(KB2SEQ_ERR_VALUE, "gla: key size %d > 1024", dk);
   if (H > 65535) return failf(KB2SEQ_ERR_VALUE, "gla: too many heads");
+  const bool aligned = ((uintptr_t)qkv & 15) == 0 && (ld & 3) == 0 && (q_off & 3) == 0 && (k_off & 3) == 0 && (v_off & 3) == 0 &&
+                       scratch != nullptr && ((uintptr_t)scratch & 15) == 0;
+  if (aligned && (dk == 32 || dk == 64 || dk == 128 || dk == 256) && dv % 32 == 0 && dv / 32 <= 65535) {
+    cudaStream_t st0 = (cudaStream_t)stream;
+    const long long ne = (long long)T * H * dk;
+    gla_decay_kernel<<<(unsigned)((ne + 255) / 256), 256, 0, st0>>>(decay_in, lda, decay_bias, 1.f / tau, T, H * dk, scratch);
+    SEQ_LAUNCHED();
+    if (dk == 32) return launch_gla_reg<32>(qkv, ld, q_off, k_off, v_off, scratch, q_scale, S, H, dv, state, cu, slots, out, st0);
+    if (dk == 64) return launch_gla_reg<64>(qkv, ld, q_off, k_off, v_off, scratch, q_scale, S, H, dv, state, cu, slots, out, st0);
+    if (dk == 128) return launch_gla_reg<128>(qkv, ld, q_off, k_off, v_off, scratch, q_scale, S, H, dv, state, cu, slots, out, st0);
+    return launch_gla_reg<256>(qkv, ld, q_off, k_off, v_off, scratch, q_scale, S, H, dv, state, cu, slots, out, st0);
+  }
   // P lanes share a value column; each keeps at most 32 (16 for small heads) of its rows
   int P = 1;
   while ((dk + P - 1) / P > 32) P <<= 1;
@@ -305,13 +458,14 @@ KB2SEQ_API int kb2_seq_selective_scan(const float* x, long long ldx, const float
   const int NR = N <= 32 ? 1 : (N <= 64 ? 2 : (N <= 128 ? 4 : 8));
   const int P = pow2_at_least((N + NR - 1) / NR);
   const int CB = (kRecThreads / 32) * (32 / P);
-  const size_t smem = (size_t)(2 * kRecTok * N + 2 * kRecTok * CB) * 4;
+  const size_t smem = (size_t)(2 * kRecTok * 2 * N + 3 * 2 * kRecTok * CB + kRecTok * kRecThreads) * 4;
   dim3 grid(S, (inner + CB - 1) / CB);
   cudaStream_t st = (cudaStream_t)stream;
 #define KB2_SCAN(NRV)                                                                                                                  \
+  if (smem > 48 * 1024) SEQ_CUDA(cudaFuncSetAttribute(selective_scan_kernel<NRV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
   selective_scan_kernel<NRV><<<grid, kRecThreads, smem, st>>>(x, ldx, dt_in, ldd, dt_bias, bc, ldb, b_off, z, ldz, z_off, A_log, D, inner, N, \
                                                               P, state, cu, slots, out, dt_out)
-  if (NR == 1) KB2_SCAN(1); else if (NR == 2) KB2_SCAN(2); else if (NR == 4) KB2_SCAN(4); else KB2_SCAN(8);
+  if (NR == 1) { KB2_SCAN(1); } else if (NR == 2) { KB2_SCAN(2); } else if (NR == 4) { KB2_SCAN(4); } else { KB2_SCAN(8); }
 #undef KB2_SCAN
   SEQ_LAUNCHED();
   return KB2SEQ_OK;

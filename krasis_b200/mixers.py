@@ -263,11 +263,16 @@ class GatedLinearAttention:
         self.q_off, self.k_off, self.v_off = 0, heads * dim, 2 * heads * dim
         self.g_off = self.v_off + heads * vdim
         self.a_off = self.g_off + heads * vdim
-        self.w_in = d(torch.cat([weights[k] for k in ("q", "k", "v", "g", "a1")], 0))        # one projection of the layer input
+        rows = [weights[k] for k in ("q", "k", "v", "g", "a1")]
+        pad = -sum(r.shape[0] for r in rows) % 4                                              # rows of the product start on 16 bytes
+        if pad:
+            rows.append(torch.zeros(pad, rows[0].shape[1], dtype=rows[0].dtype))
+        self.w_in = d(torch.cat(rows, 0))                                                     # one projection of the layer input
         self.w_a2, self.a2_b, self.norm = d(weights["a2"]), f(weights["a2_b"]), f(weights["norm"])
         if self.w_a2.shape[0] != heads * dim or self.a2_b.numel() != heads * dim or self.norm.numel() != vdim:
             raise ValueError("decay projection / norm do not match heads x dim / vdim")
         self.w_o = d(weights["o"])
+        self.register_state_kernel = dim in (32, 64, 128, 256) and vdim % 32 == 0
 
     def register_state(self, pool):
         """Recurrent state [slots, H, dk, dv] in a RecurrentStatePool."""
@@ -278,9 +283,12 @@ class GatedLinearAttention:
         proj = lin(h, self.w_in, torch.float32)
         dec_in = lin_cols(proj, self.a_off, self.ra, self.w_a2, self.dtype)                   # [T, H dk]
         o = torch.empty((T, H * self.dv), dtype=torch.float32, device=h.device)
+        # key sizes 32 / 64 / 128 / 256 with value sizes that are multiples of 32 keep the state in registers (the decays meet in scratch)
+        scratch = torch.empty((T, H * self.dk), dtype=torch.float32, device=h.device) if self.register_state_kernel else None
         ops.check(lib.kb2_seq_gla(proj.data_ptr(), proj.stride(0), self.q_off, self.k_off, self.v_off, dec_in.data_ptr(), dec_in.stride(0),
                                   self.a2_b.data_ptr(), self.tau, self.q_scale, T, tb.S, H, self.dk, self.dv, state.data_ptr(),
-                                  tb.cu.data_ptr(), tb.slots.data_ptr(), o.data_ptr(), torch.cuda.current_stream(h.device).cuda_stream))
+                                  tb.cu.data_ptr(), tb.slots.data_ptr(), ops._ptr(scratch), o.data_ptr(),
+                                  torch.cuda.current_stream(h.device).cuda_stream))
         o = ops.head_norm_gate(o, H, self.dv, self.dtype, norm=self.norm, eps=self.eps, gate=proj[:, self.g_off:], gate_act="silu")
         return lin(o, self.w_o, torch.float32)
 

@@ -41,7 +41,7 @@ SIGNATURES = {
     "kb2_seq_moe_gemm": (_I, [_P, _I, _L, _P, _I, _P, _I, _L, _L, _P, _I, _L, _I, _I, _P, _P, _I, _I, _P]),
     "kb2_seq_moe_gemv": (_I, [_P, _I, _L, _I, _P, _I, _P, _I, _L, _L, _P, _I, _L, _I, _I, _I, _P]),
     "kb2_seq_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _P, _P, _I, _P, _L, _P]),
-    "kb2_seq_gla": (_I, [_P, _L, _I, _I, _I, _P, _L, _P, _F, _F, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "kb2_seq_gla": (_I, [_P, _L, _I, _I, _I, _P, _L, _P, _F, _F, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "kb2_seq_selective_scan": (_I, [_P, _L, _P, _L, _P, _P, _L, _I, _P, _L, _I, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _I, _P]),
     "kb2_seq_head_norm_gate": (_I, [_P, _L, _P, _F, _P, _L, _I, _I, _I, _I, _P, _I, _P]),
     "kb2_seq_rms_rows": (_I, [_P, _L, _I, _P, _F, _P, _I, _L, _I, _P]),

@@ -308,7 +308,8 @@ def gla_weights(m, W, seed, rank=5):
 
 
 @pytest.mark.parametrize("m", [gla(), gla(heads=1, dim=40, vdim=36, tau=1.0), gla(heads=2, dim=128, vdim=32, tau=16.0),
-                               gla(heads=5, dim=1, vdim=3, tau=2.5), gla(heads=2, dim=70, vdim=130, tau=8.0)])
+                               gla(heads=5, dim=1, vdim=3, tau=2.5), gla(heads=2, dim=70, vdim=130, tau=8.0),
+                               gla(heads=3, dim=32, vdim=96, tau=2.0), gla(heads=2, dim=64, vdim=64, tau=16.0), gla(heads=1, dim=256, vdim=32, tau=5.0)])
 def test_gated_linear_attention_alone(seq, m):
     from krasis_b200.mixers import GatedLinearAttention
     W, T = 48, 41
@@ -316,6 +317,7 @@ def test_gated_linear_attention_alone(seq, m):
     h = rnd(T, W, seed=5)
     want = O.gated_linear_attention(h.numpy().astype(np.float64), f64(w), m, EPS)
     mixer = GatedLinearAttention(under(w), m["heads"], m["dim"], m["vdim"], m["tau"], EPS, torch.float32, torch.device(DEV))
+    assert mixer.register_state_kernel == (m["dim"] in (32, 64, 128, 256) and m["vdim"] % 32 == 0)      # both forms of the kernel are covered
     for cuts in CUTS:
         one = OneSequence(seq, (1, 1), 4, T, register=mixer.register_state)
         got = np.concatenate([mixer.forward(h[at:at + n].to(DEV).contiguous(), tb, one.state).cpu().numpy() for at, n, tb in one.portions(T, cuts)], 0)
