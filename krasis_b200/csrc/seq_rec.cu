@@ -217,7 +217,7 @@ __global__ void __launch_bounds__(kRecThreads) selective_scan_kernel(const float
   float* dts = bcs + 2 * kRecTok * 2 * N;            // [2][kRecTok][CB]: dt input, then the step size
   float* xs = dts + 2 * kRecTok * CB;                // [2][kRecTok][CB]
   float* zs = xs + 2 * kRecTok * CB;                 // [2][kRecTok][CB]
-  float* yp = zs + 2 * kRecTok * CB;                 // [kRecTok][threads]: every lane's piece of y, summed once per tile
+  float* yp = zs + 2 * kRecTok * CB;                 // [kRecTok][CB][P + 1]: every lane's piece of y, summed once per tile (odd pitch: no bank conflicts)
   const int s = blockIdx.x, c0 = blockIdx.y * CB;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int p = lane % P, cl = warp * CW + lane / P, c = c0 + cl;   // tid == cl * P + p
@@ -279,13 +279,13 @@ __global__ void __launch_bounds__(kRecThreads) selective_scan_kernel(const float
             y = fmaf(st[ii], row[N + j], y);
           }
         }
-        yp[tt * kRecThreads + tid] = y;
+        yp[(tt * CB + cl) * (P + 1) + p] = y;
       }
     }
     __syncthreads();
     for (int e = tid; e < nt * ncb; e += kRecThreads) {
       const int tt = e / ncb, cc = e - tt * ncb;
-      const float* pieces = yp + tt * kRecThreads + cc * P;
+      const float* pieces = yp + (tt * CB + cc) * (P + 1);
       float y = 0.f;
       for (int q = 0; q < P; ++q) y += pieces[q];
       const int src = (buf * kRecTok + tt) * CB + cc;
@@ -458,7 +458,7 @@ KB2SEQ_API int kb2_seq_selective_scan(const float* x, long long ldx, const float
   const int NR = N <= 32 ? 1 : (N <= 64 ? 2 : (N <= 128 ? 4 : 8));
   const int P = pow2_at_least((N + NR - 1) / NR);
   const int CB = (kRecThreads / 32) * (32 / P);
-  const size_t smem = (size_t)(2 * kRecTok * 2 * N + 3 * 2 * kRecTok * CB + kRecTok * kRecThreads) * 4;
+  const size_t smem = (size_t)(2 * kRecTok * 2 * N + 3 * 2 * kRecTok * CB + kRecTok * CB * (P + 1)) * 4;
   dim3 grid(S, (inner + CB - 1) / CB);
   cudaStream_t st = (cudaStream_t)stream;
 #define KB2_SCAN(NRV)                                                                                                                  \
