@@ -374,6 +374,13 @@ KB2_API int kb2_fmha_maps_softcap(const void* q_dev, const void* k_dev, const vo
                                   int32_t kv_len, int32_t num_q, int32_t num_kv_heads, int32_t maps, int32_t v_dim, float sm_scale,
                                   float softcap, int32_t window, int32_t device, void* stream);
 
+/* The same with a softmax sink per query vector (sinks_dev fp32 [num_q], may be null: exp(sink) joins the denominator, no value) and,
+ * if lse_dev (fp32 [M][num_q]) is given, the logarithm of every row's softmax denominator written out, so that a caller can merge
+ * further keys into the same softmax. */
+KB2_API int kb2_fmha_maps_sink(const void* q_dev, const void* k_dev, const void* v_dev, float* out_dev, int32_t M, int32_t q_start,
+                               int32_t kv_len, int32_t num_q, int32_t num_kv_heads, int32_t maps, int32_t v_dim, float sm_scale,
+                               float softcap, int32_t window, const float* sinks_dev, float* lse_dev, int32_t device, void* stream);
+
 /* GEMM -> reduce-scatter fused (head-parallel attention under token sharding): after kb2_{gdn,gqa,mla}_set_output_scatter the
  * block's out_proj GEMM stores every output row straight into the receive buffer of the rank that owns the token
  * (peer_recv_host[r] from kb2_comm_peer_alloc, layout [M / num_ranks][num_ranks][hidden] bf16, slot = src_rank) instead of out_dev

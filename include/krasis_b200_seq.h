@@ -139,7 +139,14 @@ KB2SEQ_API int kb2_seq_paged_attn(const float* proj, long long ldp, int T, int H
                                   const void* vc, int dt_cache, const int* positions, const int* seq_of, const int* pages, int max_pages,
                                   int page_size, float scale, int chunk, int window, float* out, int nsplit, float* part_acc,
                                   float* part_ml, const int* cu, int skip_from, float softcap, const float* sinks, int pool, const void* kp,
-                                  const void* vp, void* stream);
+                                  const void* vp, int pool_only, void* stream);
+
+/* pool_only 1 (above; needs cu, nsplit 1 and the piece buffers): the pass that follows a tensor-core attention over the window of long
+ * portions — only the tokens of sequences whose portion has skip_from tokens or more, only their pooled blocks, no sink; the result stays
+ * an unnormalised piece in part_acc [T H][dv] / part_ml [T H][2].  kb2_seq_pool_merge joins it to the window's result a [T, H, dv]
+ * (normalised, with lse [T, H] the logarithm of its softmax denominator), in place, for the same sequences (M == 1). */
+KB2SEQ_API int kb2_seq_pool_merge(float* a, const float* lse, const float* part_acc, const float* part_ml, int T, int H, int dv,
+                                  const int* seq_of, const int* cu, int min_portion, void* stream);
 
 /* out[t, h, :] = f * sum_m coef[m] a[t, h, m, :] (coef null: ones), f = post_scale / rms(sum) if unit_norm, times sigmoid(gate[t * ldg + h])
  * if gate is given (gate_wide 1: one gate per output element, sigmoid(gate[t * ldg + h dv + c])).  nsplit > 1: a is merged from

@@ -112,6 +112,7 @@ SIGNATURES = {
     "kb2_linear_bf16_grouped": (C.c_int, [C.c_void_p] * 3 + [C.c_int32] * 4 + [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "kb2_fmha_maps": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 7 + [C.c_float, C.c_int32, C.c_int32, C.c_void_p]),
     "kb2_fmha_maps_softcap": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 7 + [C.c_float, C.c_float, C.c_int32, C.c_int32, C.c_void_p]),
+    "kb2_fmha_maps_sink": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 7 + [C.c_float, C.c_float, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "kb2_comm_unique_id": (C.c_int, [C.c_void_p]),
     "kb2_comm_init": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
     "kb2_comm_destroy": (None, [C.c_void_p]),

@@ -48,7 +48,7 @@ cudaError_t launch_gqa_core(const GqaDims& g, const void* q_raw, const void* k_r
 cudaError_t launch_fmha_latent(const void* q, const void* kv_up, const void* kpe, void* out, int M, int q_start, int kv_len, int nh,
                                float sm_scale, int window, const float* sinks, cudaStream_t s);
 cudaError_t launch_fmha_maps(const void* q, const void* k, const void* v, float* out_f32, int M, int q_start, int kv_len, int nq, int nkv,
-                             int maps, int dv, float sm_scale, int window, cudaStream_t s, float softcap = 0.f);
+                             int maps, int dv, float sm_scale, int window, cudaStream_t s, float softcap = 0.f, const float* sinks = nullptr, float* lse_out = nullptr);
 struct MlaDims {
   int H, nh, nope, rope, dv, lora;
   float eps;
@@ -669,6 +669,20 @@ KB2_API int kb2_fmha_maps_softcap(const void* q_dev, const void* k_dev, const vo
   CUDA_TRY(cudaSetDevice(device));
   CUDA_TRY(launch_fmha_maps(q_dev, k_dev, v_dev, out_dev, M, q_start, kv_len, num_q, num_kv_heads, maps, v_dim, sm_scale, window,
                             (cudaStream_t)stream, softcap));
+  return KB2_OK;
+}
+
+KB2_API int kb2_fmha_maps_sink(const void* q_dev, const void* k_dev, const void* v_dev, float* out_dev, int32_t M, int32_t q_start,
+                               int32_t kv_len, int32_t num_q, int32_t num_kv_heads, int32_t maps, int32_t v_dim, float sm_scale,
+                               float softcap, int32_t window, const float* sinks_dev, float* lse_dev, int32_t device, void* stream) {
+  if (!q_dev || !k_dev || !v_dev || !out_dev) return failf(KB2_ERR_VALUE, "null argument");
+  if (M <= 0 || num_q <= 0 || num_kv_heads <= 0 || maps <= 0 || num_q % maps || (num_q / maps) % num_kv_heads || q_start < 0 ||
+      kv_len != q_start + M || window <= 0 || (v_dim != 128 && v_dim != 256) || !(softcap >= 0.f) || !(sm_scale > 0.f))
+    return failf(KB2_ERR_VALUE, "fmha_maps: need M > 0, kv_len == q_start + M, window > 0, value size 128 or 256, scale > 0, softcap >= 0 (M=%d q_start=%d kv_len=%d dv=%d)",
+                 M, q_start, kv_len, v_dim);
+  CUDA_TRY(cudaSetDevice(device));
+  CUDA_TRY(launch_fmha_maps(q_dev, k_dev, v_dev, out_dev, M, q_start, kv_len, num_q, num_kv_heads, maps, v_dim, sm_scale, window,
+                            (cudaStream_t)stream, softcap, sinks_dev, lse_dev));
   return KB2_OK;
 }
 

@@ -184,8 +184,10 @@ __global__ void __launch_bounds__(kFThreads, 1)
                     int maps = 1,                                // query heads come in groups of `maps` attention maps: map m of a head reads
                                                                  // key head kvh * maps + m, every map reads value head kvh
                     float* __restrict__ out_f32 = nullptr,       // if given, the output rows are written here in fp32 (no gate), not to `out`
-                    float cap_in = 0.f, float cap_out = 0.f) {   // soft cap: a raw score s becomes cap_out * tanh(s * cap_in) with
+                    float cap_in = 0.f, float cap_out = 0.f,     // soft cap: a raw score s becomes cap_out * tanh(s * cap_in) with
                                                                  // cap_in = sm_scale / cap, cap_out = cap / sm_scale (0: no cap)
+                    float* __restrict__ lse_out = nullptr) {     // if given, [M][nh]: log(sum of exp(scaled scores)) of every row (the sink
+                                                                 // included), so that a caller can merge further keys into the softmax
   using L = FmhaSmem<DQ, DV>;
   constexpr int D = DQ;
   constexpr int NC = DQ / 64;                      // 64-wide d chunks of q/k
@@ -454,6 +456,8 @@ __global__ void __launch_bounds__(kFThreads, 1)
       xb[hf * kFQ + row] = l_sum;
       named_bar_sync(1 + q, 64);
       l_sum += xb[(hf ^ 1) * kFQ + row];
+      if (lse_out != nullptr && hf == 0 && qi < M)
+        lse_out[(long long)qi * g.nh + head] = l_sum > 0.f ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
       if (n_tiles >= 2) pv_wait((n_tiles - 2) & 1, (uint32_t)((n_tiles - 2) / 2 + 1));
       pv_wait((n_tiles - 1) & 1, (uint32_t)((n_tiles - 1) / 2 + 1));
       const float inv_l = l_sum > 0.f ? 1.0f / l_sum : 0.f;
@@ -753,9 +757,10 @@ cudaError_t launch_fmha_latent(const void* q, const void* kv_up, const void* kpe
 // Attention core on dense BF16 rows for heads that carry several attention maps: q [M][nq * 128] with nq = heads * maps query
 // vectors (head by head, map by map), k [kv_len][nkv * maps * 128], v [kv_len][nkv * dv], dv 128 or 256; out_f32 [M][nq * dv] fp32.
 // Query i stands at position q_start + i of the kv rows and sees the keys with 0 <= position - key < window.
-// softcap > 0: a scaled score s becomes softcap * tanh(s / softcap).
+// softcap > 0: a scaled score s becomes softcap * tanh(s / softcap).  sinks (fp32 [nq], may be null): exp(sink) joins each query vector's
+// softmax denominator.  lse_out (fp32 [M][nq], may be null): the logarithm of that denominator per row.
 cudaError_t launch_fmha_maps(const void* q, const void* k, const void* v, float* out_f32, int M, int q_start, int kv_len, int nq, int nkv,
-                             int maps, int dv, float sm_scale, int window, cudaStream_t s, float softcap) {
+                             int maps, int dv, float sm_scale, int window, cudaStream_t s, float softcap, const float* sinks, float* lse_out) {
   if (!(softcap >= 0.f) || !(sm_scale > 0.f)) return cudaErrorInvalidValue;
   const float cap_in = softcap > 0.f ? sm_scale / softcap : 0.f, cap_out = softcap > 0.f ? softcap / sm_scale : 0.f;
   if (M <= 0 || nq <= 0 || nkv <= 0 || maps <= 0 || nq % maps || (nq / maps) % nkv || q_start < 0 || kv_len != q_start + M || window <= 0 ||
@@ -782,10 +787,10 @@ cudaError_t launch_fmha_maps(const void* q, const void* k, const void* v, float*
   const float sl2 = sm_scale * 1.4426950408889634f;
   if (dv == 256)
     gqa_fmha_kernel<128, 256, false><<<grid, kFThreads, FmhaSmem<128, 256>::kTotal, s>>>(tq, tk, tk, tv, g, nullptr, nullptr, M, q_start, kv_len,
-                                                                                          sl2, 0, 0, window, nullptr, maps, out_f32, cap_in, cap_out);
+                                                                                          sl2, 0, 0, window, sinks, maps, out_f32, cap_in, cap_out, lse_out);
   else
     gqa_fmha_kernel<128, 128, false><<<grid, kFThreads, FmhaSmem<128, 128>::kTotal, s>>>(tq, tk, tk, tv, g, nullptr, nullptr, M, q_start, kv_len,
-                                                                                          sl2, 0, 0, window, nullptr, maps, out_f32, cap_in, cap_out);
+                                                                                          sl2, 0, 0, window, sinks, maps, out_f32, cap_in, cap_out, lse_out);
   return cudaGetLastError();
 }
 

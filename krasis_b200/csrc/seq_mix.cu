@@ -165,12 +165,14 @@ __global__ void __launch_bounds__(kPAThreads) paged_attn_kernel(
     const void* __restrict__ vc, int dt_cache, const int* __restrict__ positions, const int* __restrict__ seq_of,
     const int* __restrict__ pages, int max_pages, int page_size, float scale, int chunk, int window, float* __restrict__ out, int nsplit,
     float* __restrict__ part_acc, float* __restrict__ part_ml, const int* __restrict__ cu, int skip_from, float softcap,
-    const float* __restrict__ sinks, int pool, int rows_per_page, const void* __restrict__ kp, const void* __restrict__ vp) {
+    const float* __restrict__ sinks, int pool, int rows_per_page, const void* __restrict__ kp, const void* __restrict__ vp, int pool_only) {
   extern __shared__ __align__(16) float sm[];
   constexpr int KT = kPAKT;
   const long long t = blockIdx.x;
   const int seq = seq_of[t];
-  if (cu != nullptr && cu[seq + 1] - cu[seq] >= skip_from) return;      // served by the tensor-core kernel
+  // long portions are served by the tensor-core kernel; pool_only is the second pass over exactly those: the pooled blocks alone, left
+  // as an unnormalised piece (running maximum, sum, weighted values) that pool_merge joins to the tensor-core result
+  if (cu != nullptr && (cu[seq + 1] - cu[seq] >= skip_from) != (pool_only != 0)) return;
   const int R = (H / G) * M, nrb = (R + RB - 1) / RB;
   const int g = blockIdx.y / nrb, r0 = (blockIdx.y - g * nrb) * RB, nr = min(RB, R - r0);
   const int KD = M * d, KP = KD | 1;         // odd row pitch: a lane per key reads without bank conflicts
@@ -190,7 +192,7 @@ __global__ void __launch_bounds__(kPAThreads) paged_attn_kernel(
   }
   const int z = blockIdx.z;
   if (tid < nr) {          // a sink is a key without a value: the running maximum starts at it, the running sum at 1 (first piece only)
-    const bool sk = sinks != nullptr && z == 0;
+    const bool sk = sinks != nullptr && z == 0 && !pool_only;
     m_run[tid] = sk ? sinks[g * (H / G) + (r0 + tid) / M] : -INFINITY;
     l_run[tid] = sk ? 1.f : 0.f;
   }
@@ -202,7 +204,7 @@ __global__ void __launch_bounds__(kPAThreads) paged_attn_kernel(
   // the keys of a token, in order: the pooled blocks that lie wholly before the window (block b: b pool + pool - 1 <= pos - window),
   // then the positions j_lo .. pos.  Index u of that list: u < nb is block u, else position j_lo + u - nb.
   const int nb = pool > 0 ? max(0, pos - window + 1) / pool : 0;
-  const int total = nb + pos - j_lo + 1;
+  const int total = pool_only ? nb : nb + pos - j_lo + 1;
   int u_begin = 0, u_end = total - 1;
   if (nsplit > 1) {
     const int piece = ((total + nsplit - 1) / nsplit + KT - 1) / KT * KT;
@@ -296,11 +298,11 @@ __global__ void __launch_bounds__(kPAThreads) paged_attn_kernel(
     const int i = tid + a * kPAThreads;
     if (i < nr * dv) {
       const int r = i / dv, c = i - r * dv;
-      if (nsplit > 1) part_acc[((row0 + r) * nsplit + z) * dv + c] = acc[a];
+      if (nsplit > 1 || pool_only) part_acc[((row0 + r) * nsplit + z) * dv + c] = acc[a];
       else out[(row0 + r) * dv + c] = acc[a] / l_run[r];
     }
   }
-  if (nsplit > 1 && tid < nr) {
+  if ((nsplit > 1 || pool_only) && tid < nr) {
     part_ml[((row0 + tid) * nsplit + z) * 2] = m_run[tid];
     part_ml[((row0 + tid) * nsplit + z) * 2 + 1] = l_run[tid];
   }
@@ -408,6 +410,26 @@ __global__ void __launch_bounds__(256) attn_finish_kernel(const float* __restric
       st_dt(out, dt_out, w * dv + c, v);
     }
   }
+}
+
+// a[t, h, :] is a normalised attention output whose softmax denominator has the logarithm lse[t, h]; (part_acc, part_ml) is an
+// unnormalised piece over further keys (running maximum m, sum l, weighted values).  Both are joined into one softmax, in place.
+// A warp per (token, head); only sequences whose portion has at least min_portion tokens.
+__global__ void __launch_bounds__(256) pool_merge_kernel(float* __restrict__ a, const float* __restrict__ lse, const float* __restrict__ part_acc,
+                                                         const float* __restrict__ part_ml, long long rows, int H, int dv,
+                                                         const int* __restrict__ seq_of, const int* __restrict__ cu, int min_portion) {
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= rows) return;
+  const int sq = seq_of[w / H];
+  if (cu[sq + 1] - cu[sq] < min_portion) return;
+  const float mp = part_ml[w * 2], lp = part_ml[w * 2 + 1];
+  if (!(lp > 0.f)) return;                              // no pooled block is visible yet
+  const float lw = lse[w];
+  const float top = fmaxf(lw, mp);
+  const float ww = lw == -INFINITY ? 0.f : expf(lw - top), wp = expf(mp - top);
+  const float inv = 1.f / (ww + lp * wp);
+  for (int c = lane; c < dv; c += 32) a[w * dv + c] = (a[w * dv + c] * ww + part_acc[w * dv + c] * wp) * inv;
 }
 
 // ------------------------------------------------------------------------------------------------ gated linear units
@@ -770,8 +792,10 @@ KB2SEQ_API int kb2_seq_paged_attn(const float* proj, long long ldp, int T, int H
                                   const void* vc, int dt_cache, const int* positions, const int* seq_of, const int* pages, int max_pages,
                                   int page_size, float scale, int chunk, int window, float* out, int nsplit, float* part_acc,
                                   float* part_ml, const int* cu, int skip_from, float softcap, const float* sinks, int pool, const void* kp,
-                                  const void* vp, void* stream) {
+                                  const void* vp, int pool_only, void* stream) {
   if (pool < 0 || (pool > 0 && (!kp || !vp || chunk > 0))) return failf(KB2SEQ_ERR_VALUE, "paged_attn: pooled blocks need their pools and no chunks");
+  if (pool_only && (pool <= 0 || nsplit != 1 || !part_acc || !part_ml || !cu))
+    return failf(KB2SEQ_ERR_VALUE, "paged_attn: the pass over the pooled blocks alone needs pool > 0, one key piece, the piece buffers and cu");
   if (!proj || !kc || !vc || !positions || !seq_of || !pages || !out || T <= 0 || H <= 0 || G <= 0 || H % G || M <= 0 || d <= 0 ||
       dv <= 0 || window <= 0 || chunk < 0 || page_size <= 0 || bad_dt(dt_cache) || !(softcap >= 0.f))
     return failf(KB2SEQ_ERR_VALUE, "paged_attn: bad argument");
@@ -790,7 +814,16 @@ KB2SEQ_API int kb2_seq_paged_attn(const float* proj, long long ldp, int T, int H
   if ((long long)G * nrb > 65535) return failf(KB2SEQ_ERR_VALUE, "paged_attn: too many heads");
   paged_attn_kernel<<<dim3(T, G * nrb, nsplit), kPAThreads, smem, (cudaStream_t)stream>>>(
       proj, ldp, H, G, M, d, dv, RB, kc, vc, dt_cache, positions, seq_of, pages, max_pages, page_size, scale, chunk, window, out, nsplit,
-      part_acc, part_ml, cu, skip_from, softcap, sinks, pool, pool > 0 ? (page_size + pool - 1) / pool : 0, kp, vp);
+      part_acc, part_ml, cu, skip_from, softcap, sinks, pool, pool > 0 ? (page_size + pool - 1) / pool : 0, kp, vp, pool_only);
+  SEQ_LAUNCHED();
+  return KB2SEQ_OK;
+}
+
+KB2SEQ_API int kb2_seq_pool_merge(float* a, const float* lse, const float* part_acc, const float* part_ml, int T, int H, int dv,
+                                  const int* seq_of, const int* cu, int min_portion, void* stream) {
+  if (!a || !lse || !part_acc || !part_ml || !seq_of || !cu || T <= 0 || H <= 0 || dv <= 0) return failf(KB2SEQ_ERR_VALUE, "pool_merge: bad argument");
+  const long long rows = (long long)T * H;
+  pool_merge_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, (cudaStream_t)stream>>>(a, lse, part_acc, part_ml, rows, H, dv, seq_of, cu, min_portion);
   SEQ_LAUNCHED();
   return KB2SEQ_OK;
 }

@@ -531,7 +531,8 @@ class MultiMapAttention:
         # long prompt portions in bfloat16 with 128 query / key dims per map and 128 or 256 value dims run the tcgen05 attention core of
         # the MoE prefill models, one call per chunk the portion touches, on keys and values gathered from the pages
         self.tc_min_portion = 128
-        self.tc_shape = dtype == torch.bfloat16 and dim == 128 and vdim in (128, 256) and self.sink is None and not self.pool
+        # (a sink goes into the core's softmax; pooled blocks are a second pass on the plain kernel, merged by the two log-sum-exps)
+        self.tc_shape = dtype == torch.bfloat16 and dim == 128 and vdim in (128, 256) and (self.M == 1 or (self.sink is None and not self.pool))
 
     def cache_dims(self):
         """(key width, value width) of a cache row; with pooled blocks a third entry, the block length."""
@@ -541,7 +542,7 @@ class MultiMapAttention:
         """Convolution tail [slots, C, taps - 1] in a RecurrentStatePool (None without a convolution)."""
         return pool.register(self.C, max(self.K - 1, 1)) if self.K else None
 
-    def _tensor_core_portion(self, core, proj, a, tb, i, kc, vc, page_size, stream):
+    def _tensor_core_portion(self, core, proj, a, tb, i, kc, vc, page_size, stream, lse=None):
         """Sequence i of the step on the tcgen05 kernel: a[rows of the portion] = per-map attention outputs (fp32)."""
         import numpy as np
         from . import capi
@@ -564,9 +565,16 @@ class MultiMapAttention:
             end = min(start + n, cstart + chunk) if chunk else start + n
             lo = max(cstart, first)
             m = end - pos
-            capi.check(core.kb2_fmha_maps_softcap(q[pos - start:].data_ptr(), k_rows[lo - first:].data_ptr(), v_rows[lo - first:].data_ptr(),
-                                                  a[row0 + pos - start:].data_ptr(), m, pos - lo, end - lo, H * M, G, M, dv, self.scale,
-                                                  self.softcap, min(self.window, 1 << 30), proj.device.index or 0, stream))
+            if self.sink is not None or lse is not None:
+                capi.check(core.kb2_fmha_maps_sink(q[pos - start:].data_ptr(), k_rows[lo - first:].data_ptr(), v_rows[lo - first:].data_ptr(),
+                                                   a[row0 + pos - start:].data_ptr(), m, pos - lo, end - lo, H * M, G, M, dv, self.scale,
+                                                   self.softcap, min(self.window, 1 << 30), ops._ptr(self.sink),
+                                                   lse[row0 + pos - start:].data_ptr() if lse is not None else None,
+                                                   proj.device.index or 0, stream))
+            else:
+                capi.check(core.kb2_fmha_maps_softcap(q[pos - start:].data_ptr(), k_rows[lo - first:].data_ptr(), v_rows[lo - first:].data_ptr(),
+                                                      a[row0 + pos - start:].data_ptr(), m, pos - lo, end - lo, H * M, G, M, dv, self.scale,
+                                                      self.softcap, min(self.window, 1 << 30), proj.device.index or 0, stream))
             pos = end
 
     def forward(self, h: torch.Tensor, tb: ops.StepTables, kc: torch.Tensor, vc: torch.Tensor, page_size: int, tail=None, pooled=None) -> torch.Tensor:
@@ -608,9 +616,20 @@ class MultiMapAttention:
                                              tb.positions.data_ptr(), tb.seq_of.data_ptr(), tb.pages.data_ptr(), tb.max_pages, page_size,
                                              self.scale, self.chunk, min(self.window, 1 << 30), a.data_ptr(), nsplit, ops._ptr(part_acc),
                                              ops._ptr(part_ml), tb.cu.data_ptr() if fast else None, self.tc_min_portion, self.softcap,
-                                             ops._ptr(self.sink), self.pool, ops._ptr(kp), ops._ptr(vp), s))
+                                             ops._ptr(self.sink), self.pool, ops._ptr(kp), ops._ptr(vp), 0, s))
+        lse = torch.empty((T, H), dtype=torch.float32, device=h.device) if (fast and self.pool) else None
         for i in fast:
-            self._tensor_core_portion(core, proj, a, tb, i, kc, vc, page_size, s)
+            self._tensor_core_portion(core, proj, a, tb, i, kc, vc, page_size, s, lse=lse)
+        if fast and self.pool:                       # the pooled blocks of the long portions: a second pass, joined by the log-sum-exps
+            p_acc = torch.empty((T * H, self.dv), dtype=torch.float32, device=h.device)
+            p_ml = torch.empty((T * H, 2), dtype=torch.float32, device=h.device)
+            ops.check(lib.kb2_seq_paged_attn(proj.data_ptr(), ldp, T, H, G, M, self.d, self.dv, kc.data_ptr(), vc.data_ptr(), dtc,
+                                             tb.positions.data_ptr(), tb.seq_of.data_ptr(), tb.pages.data_ptr(), tb.max_pages, page_size,
+                                             self.scale, 0, min(self.window, 1 << 30), a.data_ptr(), 1, p_acc.data_ptr(), p_ml.data_ptr(),
+                                             tb.cu.data_ptr(), self.tc_min_portion, self.softcap, None, self.pool, kp.data_ptr(),
+                                             vp.data_ptr(), 1, s))
+            ops.check(lib.kb2_seq_pool_merge(a.data_ptr(), lse.data_ptr(), p_acc.data_ptr(), p_ml.data_ptr(), T, H, self.dv,
+                                             tb.seq_of.data_ptr(), tb.cu.data_ptr(), self.tc_min_portion, s))
         o = torch.empty((T, H * self.dv), dtype=self.dtype, device=h.device)
         gate = proj_in[:, self.gate_off:] if self.gate_off >= 0 else None
         ops.check(lib.kb2_seq_attn_finish(a.data_ptr(), ops._ptr(part_acc), ops._ptr(part_ml), nsplit, T, H, M, self.dv, ops._ptr(self.map_coef),

@@ -32,7 +32,8 @@ SIGNATURES = {
     "kb2_seq_head_kv_prep": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _P, _P]),
     "kb2_seq_kv_pool": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P]),
     "kb2_seq_paged_attn": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _F, _I, _I, _P, _I, _P, _P, _P, _I, _F, _P, _I,
-                                _P, _P, _P]),
+                                _P, _P, _I, _P]),
+    "kb2_seq_pool_merge": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _P]),
     "kb2_seq_attn_finish": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _F, _F, _P, _L, _P, _I, _P, _P, _I, _I, _P, _P, _I, _P]),
     "kb2_seq_glu": (_I, [_P, _I, _L, _P, _I, _L, _I, _I, _F, _F, _P, _I, _P]),
     "kb2_seq_route": (_I, [_P, _L, _I, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P]),

@@ -552,3 +552,66 @@ def test_registry_loads_a_checkpoint_directory_and_the_trace_runner_replays_it(s
     assert not (out / "1.f32").exists()
     close(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, -1), want[[0, 9]], 5e-5, "step 0")
     close(np.fromfile(out / "2.f32", dtype="<f4").reshape(2, -1), want[[24, 2]], 5e-5, "step 2")
+
+
+def test_tensor_core_prefill_with_sink_pooled_blocks_and_rotated_values(seq):
+    """bfloat16 with 128 query / key dims and 128 or 256 value dims: portions of 128 tokens or more run the tcgen05 attention core — the
+    sink inside it, the pooled blocks as a second pass joined by the two log-sum-exps, the values rotated before the cache and turned
+    back after the core.  Against the oracle and against the plain kernels on the same bf16 cache."""
+    from krasis_b200.build import build as build_core
+    build_core()
+    # (a) one mixer with peaked scores: the last token scores members of the newest seen block, of a far block and of its window far above
+    # the rest, so that a lost or mis-weighted block moves the output by far more than the bf16 tolerance
+    W = d = 128
+    T, size, pool = 400, 100, 32
+    m = left(heads=2, kv_heads=1, dim=d, vdim=128, size=size, pool=pool, rot_dims=0, scale=1.0)
+    i = T - 1
+    newest = O.pooled_blocks(i, size, pool)[-1]
+    marks = {3: 0.7 * pool, newest * pool + 5: 0.6 * pool, newest * pool + pool - 1: 0.9 * pool, i - 1: 1.2, i - size + 1: 1.5, i - size: 1.7}
+    w = left_weights(m, W, seed=21, kind="parallel")
+    w["q"], w["k"] = torch.cat([torch.eye(d), torch.eye(d)], 0), torch.eye(d)
+    w["q.b"], w["k.b"] = torch.zeros(2 * d), torch.zeros(d)
+    w["sink"] = torch.tensor([7.0, 0.5])
+    h, uu = peaked_inputs(T, W, d, marks, seed=6)
+    m["scale"] = 5.0 / uu                                   # a mark a scores about 5 a: the marked keys outweigh the hundred plain ones
+    h64 = h.numpy().astype(np.float64)
+    want = O.grouped_window_attention(h64, f64(w), dict(m, halves=True), EPS, list(range(T)))
+    for wrong in (dict(m, mask={"size": size}), dict(m, mask={"size": size + 1, "pool": pool})):
+        off = O.grouped_window_attention(h64, f64(w), dict(wrong, halves=True), EPS, list(range(T)))
+        assert np.abs(off[i] - want[i]).max() > 0.1 * np.abs(want[i]).max()
+    nosink = dict(f64(w))
+    del nosink["sink"]
+    assert np.abs(O.grouped_window_attention(h64, nosink, dict(m, halves=True), EPS, list(range(T)))[i] - want[i]).max() > 0.1 * np.abs(want[i]).max()
+    mixer = make_left(m, w, "parallel", dtype=torch.bfloat16)
+    assert mixer.tc_shape
+    fast = run_left(seq, mixer, h, [T], page_size=8)
+    parts = run_left(seq, mixer, h, [130, 2, T - 132], page_size=8)
+    mixer.tc_min_portion = 1 << 30
+    plain = run_left(seq, mixer, h, [T], page_size=8)
+    scale_ = np.abs(want).max()
+    for got, what in ((plain, "plain kernels"), (fast, "tensor-core prefill"), (parts, "tensor-core portions")):
+        err = np.abs(got.astype(np.float64) - want).max(-1) / scale_
+        assert err[i] <= 3e-2 and np.quantile(err, 0.9) <= 3e-2, f"{what}: last token {err[i]:.3e}, 90th percentile {np.quantile(err, 0.9):.3e}"
+    # (b) the whole model
+    layers = [P1(left(heads=2, kv_heads=1, dim=128, vdim=128, size=200, pool=48, rot_dims=64), gla(heads=2, dim=64, vdim=64)),
+              P2(left(heads=4, kv_heads=2, dim=128, vdim=256, size=300, rot_dims=32, factor=2.0), scan(inner=64, state=16, dt_rank=8, conv=4)),
+              LA(latent(heads=2, dim=128, rot_dim=64, vdim=128, kv_rank=64, q_rank=64, size=250, scale=0.07))]
+    raw = model_cfg(layers, width=64)
+    model, wm = build(raw, dtype=torch.bfloat16, seed=31)
+    assert all(model.layers[k]["mixer"].left.tc_shape for k in (0, 1)) and model.layers[2]["mixer"].tc_shape
+    tk = toks(600, raw["vocab"], 16)
+    want = O.forward(raw, wm, tk)
+
+    def most(got, ref, rel, what):
+        err = np.abs(got.astype(np.float64) - ref).max(-1) / np.abs(ref).max()
+        assert np.quantile(err, 0.9) <= rel, f"{what}: {np.quantile(err, 0.9):.3e}"
+    fast_whole = run_portions(model, tk, [600], s=sched(model, 1024))
+    fast_parts = run_portions(model, tk, [130, 257, 128, 60], s=sched(model, 1024))
+    for k in (0, 1):
+        model.layers[k]["mixer"].left.tc_min_portion = 1 << 30
+    model.layers[2]["mixer"].tc_min_portion = 1 << 30
+    plain = run_portions(model, tk, [600], s=sched(model, 1024))
+    most(plain, want, 5e-2, "plain kernels against the oracle")
+    most(fast_whole, want, 5e-2, "tensor-core prefill against the oracle")
+    most(fast_whole, plain.astype(np.float64), 3e-2, "tensor-core prefill against the plain kernels")
+    most(fast_parts, plain.astype(np.float64), 3e-2, "tensor-core portions against the plain kernels")
