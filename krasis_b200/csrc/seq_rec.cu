@@ -195,6 +195,11 @@ __global__ void __launch_bounds__(32 * kGlaWarps) gla_reg_kernel(const float* __
 // x [T, ldx] (inner channels after convolution and activation), dt_in [T, ldd] (+ dt_bias, then softplus), bc [T, ldb] = [B: N | C: N]
 // from b_off, z [T, ldz] from z_off, A_log [inner, N], D [inner].  Block (sequence, group of CB channels); lane l: state slice
 // p = l % P, channel l / P of the warp; thread states are n = p + P ii, ii < NR.
+__device__ __forceinline__ float ex2_approx_ftz(float x) {       // 2^x, MUFU.EX2 (2 ulp, as exp2f); results below 2^-126 become 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void rec_cp_async4(void* smem_dst, const void* gmem_src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
 }
@@ -232,7 +237,7 @@ __global__ void __launch_bounds__(kRecThreads) selective_scan_kernel(const float
     st[ii] = ok ? S[(long long)c * N + j] : 0.f;
     a[ii] = ok ? -expf(A_log[(long long)c * N + j]) * 1.4426950408889634f : 0.f;      // A log2(e): exp(dt A) = 2^(dt a)
   }
-  const int ncb = min(CB, inner - c0);               // channels of this block that exist
+  const int cb_shift = __ffs(CB) - 1;                // CB = 256 / P is a power of two: rows and channels of a tile by shift and mask
 
   auto load_tile = [&](int buf, int b0) {
     const int nt = min(kRecTok, n - b0);
@@ -240,8 +245,9 @@ __global__ void __launch_bounds__(kRecThreads) selective_scan_kernel(const float
       const int tt = e / (2 * N), j = e - tt * 2 * N;
       rec_cp_async4(bcs + (buf * kRecTok + tt) * 2 * N + j, bc + (long long)(row0 + b0 + tt) * ldb + b_off + j);
     }
-    for (int e = tid; e < nt * ncb; e += kRecThreads) {
-      const int tt = e / ncb, cc = e - tt * ncb;
+    for (int e = tid; e < nt * CB; e += kRecThreads) {
+      const int tt = e >> cb_shift, cc = e & (CB - 1);
+      if (c0 + cc >= inner) continue;
       const long long t = row0 + b0 + tt;
       const int dst = (buf * kRecTok + tt) * CB + cc;
       rec_cp_async4(dts + dst, dt_in + t * ldd + c0 + cc);
@@ -258,33 +264,38 @@ __global__ void __launch_bounds__(kRecThreads) selective_scan_kernel(const float
     rec_cp_async_wait_all();
     __syncthreads();                                 // tile `buf` is in place; everyone is done with the other buffer and with yp
     if (t0 + kRecTok < n) load_tile(buf ^ 1, t0 + kRecTok);
-    for (int e = tid; e < nt * ncb; e += kRecThreads) {
-      const int tt = e / ncb, cc = e - tt * ncb;
-      float* d = dts + (buf * kRecTok + tt) * CB + cc;
+    for (int e = tid; e < nt * CB; e += kRecThreads) {
+      const int cc = e & (CB - 1);
+      if (c0 + cc >= inner) continue;
+      float* d = dts + buf * kRecTok * CB + e;
       *d = softplus_f(*d + dt_bias[c0 + cc]);
     }
     __syncthreads();
     if (live) {
+      const float* dp = dts + buf * kRecTok * CB + cl;
+      const float* xq = xs + buf * kRecTok * CB + cl;
+      const float* row = bcs + buf * kRecTok * 2 * N + p;
+      float* yq = yp + cl * (P + 1) + p;
+      const int ypitch = CB * (P + 1);
 #pragma unroll 4
-      for (int tt = 0; tt < nt; ++tt) {
-        const float dtv = dts[(buf * kRecTok + tt) * CB + cl];
-        const float dtx = dtv * xs[(buf * kRecTok + tt) * CB + cl];
-        const float* row = bcs + (buf * kRecTok + tt) * 2 * N;
+      for (int tt = 0; tt < nt; ++tt, dp += CB, xq += CB, row += 2 * N, yq += ypitch) {
+        const float dtv = *dp;
+        const float dtx = dtv * *xq;
         float y = 0.f;
 #pragma unroll
         for (int ii = 0; ii < NR; ++ii) {
-          const int j = p + P * ii;
-          if (j < N) {
-            st[ii] = fmaf(exp2f(dtv * a[ii]), st[ii], dtx * row[j]);
-            y = fmaf(st[ii], row[N + j], y);
+          if (p + P * ii < N) {                      // a[] is A log2(e): one MUFU per state update
+            st[ii] = fmaf(ex2_approx_ftz(dtv * a[ii]), st[ii], dtx * row[P * ii]);
+            y = fmaf(st[ii], row[N + P * ii], y);
           }
         }
-        yp[(tt * CB + cl) * (P + 1) + p] = y;
+        *yq = y;
       }
     }
     __syncthreads();
-    for (int e = tid; e < nt * ncb; e += kRecThreads) {
-      const int tt = e / ncb, cc = e - tt * ncb;
+    for (int e = tid; e < nt * CB; e += kRecThreads) {
+      const int tt = e >> cb_shift, cc = e & (CB - 1);
+      if (c0 + cc >= inner) continue;
       const float* pieces = yp + (tt * CB + cc) * (P + 1);
       float y = 0.f;
       for (int q = 0; q < P; ++q) y += pieces[q];
