@@ -3,13 +3,19 @@
 //
 //   head_kv_prep           bias, RMS norm (per vector, or one over the whole of q and one over the whole of k) and rotary positions
 //                          (pairs 2i / 2i + 1, or i / i + dims / 2) on the query and key vectors of every head and map; keys and
-//                          values go to the paged cache rows of the tokens' positions
+//                          values go to the paged cache rows of the tokens' positions; optionally the values are rotated by their
+//                          positions over all of their dimensions
+//   kv_pool                the tokens that complete a block of `pool` positions write the mean of the block's cached keys and values
+//                          into pooled pools that share the page numbering
 //   paged_attn             softmax attention of every (head, map) query vector over the cached keys of its key/value head; the maps of
 //                          a head have keys of their own and share the values; keys j <= i of the same chunk and inside the window;
-//                          optional tanh cap on the scaled scores;
+//                          optional tanh cap on the scaled scores; optional sink per head in the denominator; optionally one pooled
+//                          key / value per block that lies wholly before the window, in the same softmax;
 //                          for steps of few tokens the key range is cut into pieces that run as separate blocks
+//   pool_merge             joins the pooled blocks' piece to a tensor-core result over the window by the two log-sum-exps
 //   attn_finish            merges the pieces, combines the maps with per-map coefficients (differential attention: 1, -lambda),
-//                          unit RMS norm per head, output gate sigmoid(g) per head
+//                          unit RMS norm per head, turning rotated values back by the query's position, output gate sigmoid(g) per
+//                          head or per element
 //   glu                    act(gate) * up in three flavours (tanh-GELU, SiLU, clamped swish with up + 1), or relu^2 without an up half
 //   route_topk             scores (softmax or sigmoid) -> + correction -> best groups (by their best or two best members) -> top-k
 //                          -> weights

@@ -8,10 +8,11 @@
 //   residual_scale_rms     x += m y;  h = x / rms(x) * (shift + w)                    (the same for RMS norms and a residual multiplier)
 //   act_mul                gelu_tanh(a) * b                                           (gated feed-forward)
 //   side_gate              gelu_tanh(g) * per-layer slice of a token table            (per-layer token input)
-//   latent_prep            RMS-normed latent + rotated shared key -> paged cache, rotary on the query's rotated part (YaRN table)
-//   latent_window_attn     absorbed-form latent attention over the page list: sliding window, softmax with a per-head sink
-//   conv_silu (+ state)    short causal convolution per channel over time with a carried tail, optional bias ahead of the taps,
-//                          then SiLU or nothing; conv_run reads every input once on long steps
+//   latent_prep            RMS-normed latent + rotated shared key -> paged cache, rotary on the query's rotated part (any frequency
+//                          table); the latent columns follow the queries or come from a buffer of their own
+//   latent_window_attn     absorbed-form latent attention over the page list: sliding window, softmax with an optional per-head sink
+//   conv_silu (+ state)    short causal convolution per channel over time with a carried tail, optional bias ahead of the taps or on
+//                          their result, then SiLU or nothing; conv_run reads every input once on long steps
 //   delta_rule             gated delta rule S <- g S; u = beta (v - S^T k); S += k u^T; o = S^T q, state in fp32 slots,
 //                          unit-norm q / k, per-head RMS norm of o with a SiLU or sigmoid gate; g is one decay per head, or one
 //                          per head and key channel (it then multiplies the rows of S)
